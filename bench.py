@@ -1,0 +1,355 @@
+#!/usr/bin/env python
+"""Benchmark of the LIF fire forward+backward (BPTT) hot path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+One "step" = one forward (snn_lif_fwd) plus one backward (snn_lif_bwd) over one batch of
+synthetic input currents / upstream gradients: fp32, T=8 time steps, 2^26 neurons per GPU
+(2 GiB per tensor; the single-GPU bandwidth-sweep headline case). Inputs are i.i.d.
+N(0.5, 1) currents and N(0, 1) gradients from a fixed seed, standing in for the CIFAR /
+ImageNet activations the reference trains on.
+
+Metric: achieved HBM GB/s, counting the ALGORITHMIC bytes of the pass,
+20 B per neuron-timestep = forward (read x 4 + write spike 4) + backward (read x 4 +
+read grad 4 + write grad_x 4). With N>1 GPUs every rank processes its own 2^26-neuron shard
+(the neuron/batch axis shards with no exchange), so the aggregate is weak scaling.
+
+Printed keys beyond the base contract:
+  roofline      dominant kernel (the backward, 12 B/step) against the measured HBM copy peak
+  cpu_baseline  the PyTorch-autograd port of the reference's CPU path, timed on this host
+  e2e           same metric through the host-buffer API (pinned host -> device -> host)
+"""
+import argparse
+import json
+import os
+import statistics
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+T_STEPS = 8
+NEURONS = 1 << 26
+BYTES_FWD, BYTES_BWD = 8, 12          # algorithmic bytes per neuron-timestep, fp32
+ALPHA, THRESH, BETA, INTERVAL = 0.25, 0.25, 1.0, 0.5
+FALLBACK_HBM_GBS = 6650.0             # earlier measurement on this pool, used if no peaks file
+NOMINAL_HBM_GBS = 8000.0
+WORKLOAD = "lif_fire_fwd_bwd fp32 T=8 N=2^26 per GPU, x~N(0.5,1), grad~N(0,1), seed 1234"
+
+# DRAM traffic of the backward kernel per neuron-timestep as measured by one ncu capture
+# (dram__bytes_read.sum + dram__bytes_write.sum of snn::lif_bwd_kernel<float,4,8>, T=8,
+# N=2^24 -- 6 GiB on the device, inside the capture size rule -- divided by T*N; traffic is
+# proportional to T*N, so a full launch is this figure x T*N). None until captured.
+NCU_BWD_TRAFFIC_BYTES_PER_STEP = None
+
+
+def measured_peak():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs, device copy)"
+    except Exception:
+        return FALLBACK_HBM_GBS, "fallback (no MEASURED_PEAKS.json)"
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons of one GPU through NVML while a region runs."""
+
+    BAD = {0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown"}
+    NOTE = {0x4: "sw_power_cap", 0x80: "hw_power_brake_slowdown", 0x2: "applications_clocks_setting",
+            0x100: "display_clock_setting", 0x10: "sync_boost"}
+
+    def __init__(self, index, period=0.02):
+        self.index, self.period = index, period
+        self.samples, self.reasons = [], set()
+        self.max_mhz = None
+        self._stop = threading.Event()
+        self._thread = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self._nv = pynvml
+            self._h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self._h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self._nv = None
+
+    def _loop(self):
+        nv = self._nv
+        while not self._stop.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self._h, nv.NVML_CLOCK_SM))
+                mask = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self._h)
+                for bit, name in {**self.BAD, **self.NOTE}.items():
+                    if mask & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            self._stop.wait(self.period)
+
+    def __enter__(self):
+        if self._nv is not None:
+            self._thread = threading.Thread(target=self._loop, daemon=True)
+            self._thread.start()
+        return self
+
+    def __exit__(self, *exc):
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join()
+
+    def summary(self):
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": ["nvml unavailable"], "samples": 0}
+        return {"sm_mhz": statistics.median(self.samples), "sm_max_mhz": self.max_mhz,
+                "reasons": sorted(self.reasons), "samples": len(self.samples)}
+
+
+# ----------------------------------------------------------------------------------------------
+# CPU legs (rank 0 only): the oracle's PyTorch-autograd port of the reference's gold op, and
+# the plain-C loops, on a bounded sample of the same workload
+# ----------------------------------------------------------------------------------------------
+def cpu_torch_port_time(n_sample, reps, threads):
+    import torch
+    from oracle import lif_oracle as orc
+    torch.set_num_threads(threads)
+    gen = torch.Generator().manual_seed(1234)
+    x = 0.5 + torch.randn((T_STEPS, 1, n_sample), generator=gen)
+    g = torch.randn((T_STEPS, 1, n_sample), generator=gen)
+    best = float("inf")
+    for _ in range(reps):
+        t0 = time.perf_counter()
+        orc.torch_fire_fwd_bwd(x, g)
+        best = min(best, time.perf_counter() - t0)
+    return best
+
+
+def cpu_c_port_time(n_sample, reps):
+    import numpy as np
+    from oracle import lif_oracle as orc
+    rng = np.random.default_rng(1234)
+    x = (0.5 + rng.standard_normal((T_STEPS, 1, n_sample))).astype(np.float32)
+    g = rng.standard_normal((T_STEPS, 1, n_sample)).astype(np.float32)
+    best = float("inf")
+    for _ in range(reps):
+        t0 = time.perf_counter()
+        orc.c_lif_fwd(x)
+        orc.c_lif_bwd(x, g)
+        best = min(best, time.perf_counter() - t0)
+    return best
+
+
+def gbps(n_neurons, seconds):
+    return (BYTES_FWD + BYTES_BWD) * T_STEPS * n_neurons / seconds / 1e9
+
+
+def cpu_baseline_block():
+    cores = os.cpu_count() or 1
+    n_sample = 1 << 22
+    t_torch = cpu_torch_port_time(n_sample, reps=3, threads=cores)
+    t_c = cpu_c_port_time(1 << 24, reps=3)
+    return {
+        "value": round(gbps(n_sample, t_torch), 3), "unit": "GB/s", "cores": cores, "kind": "port",
+        "sample": f"PyTorch-autograd port of the reference's gold_fire, fwd+bwd, T=8, N=2^22 "
+                  f"(1/16 of one GPU step), best of 3, {t_torch:.3f} s",
+        "c_loops_value": round(gbps(1 << 24, t_c), 3),
+        "c_loops_sample": f"plain-C OpenMP restatement, T=8, N=2^24, best of 3, {t_c:.3f} s",
+    }
+
+
+def run_reference_arm(args):
+    """The reference's CPU implementation of the path (its pure-PyTorch gold op, restated in
+    oracle/lif_oracle.py because the reference checkout does not travel), all host threads."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    cores = os.cpu_count() or 1
+    probe = cpu_torch_port_time(1 << 18, reps=2, threads=cores)      # seconds per 2^18 neurons
+    budget = 90.0 / max(1, args.steps + args.warmup)                 # seconds per step
+    n_sample = 1 << 18
+    while n_sample < (1 << 23) and probe * (2 * n_sample / (1 << 18)) <= budget:
+        n_sample *= 2
+    import torch
+    from oracle import lif_oracle as orc
+    torch.set_num_threads(cores)
+    gen = torch.Generator().manual_seed(1234)
+    x = 0.5 + torch.randn((T_STEPS, 1, n_sample), generator=gen)
+    g = torch.randn((T_STEPS, 1, n_sample), generator=gen)
+    for _ in range(args.warmup):
+        orc.torch_fire_fwd_bwd(x, g)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        orc.torch_fire_fwd_bwd(x, g)
+    dt = (time.perf_counter() - t0) / args.steps
+    value = round(gbps(n_sample, dt), 3)
+    sample = (f"PyTorch-autograd port of the reference's gold_fire on host cores, fwd+bwd, T=8, "
+              f"N={n_sample} neurons per step (bounded sample of the 2^26-neuron step)")
+    print(json.dumps({
+        "impl": "reference", "metric": "lif_fwd_bwd_hbm_gbps", "value": value, "unit": "GB/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": round(dt * 1e3, 3), "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "sample_neurons_per_step": n_sample},
+        "cpu_baseline": {"value": value, "unit": "GB/s", "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }))
+
+
+# ----------------------------------------------------------------------------------------------
+# GPU arm
+# ----------------------------------------------------------------------------------------------
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+    from snn_gpu_training_bptt_b200 import _capi
+    from snn_gpu_training_bptt_b200.host_pipeline import HostLifPipeline
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py: no CUDA device; this benchmark has no CPU path for the product arm")
+    _capi.lib()  # fail loudly if the CUDA library is missing
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        raise SystemExit(f"bench.py: --gpus {args.gpus} but WORLD_SIZE={world}; launch with torch.distributed.run")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    T, N = T_STEPS, NEURONS
+    gen = torch.Generator(device=dev).manual_seed(1234 + rank)
+    x = torch.randn((T, 1, N), device=dev, generator=gen).add_(0.5)
+    g = torch.randn((T, 1, N), device=dev, generator=gen)
+    spike = torch.empty_like(x)
+    gx = torch.empty_like(x)
+    L = _capi.lib()
+    px, pg, ps, pgx = (_capi._ptr(t) for t in (x, g, spike, gx))
+    stream = torch.cuda.current_stream(dev)
+    sp = _capi._stream(dev)
+
+    def step():
+        _capi.check("snn_lif_fwd", L.snn_lif_fwd(px, ps, None, None, T, N, 0, ALPHA, THRESH, sp))
+        _capi.check("snn_lif_bwd", L.snn_lif_bwd(px, pg, pgx, T, N, 0, ALPHA, THRESH, BETA, INTERVAL, None, 0, sp))
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize(dev)
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    barrier()
+
+    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(args.steps)]
+    e_start, e_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(local) as clocks:
+        barrier()
+        e_start.record(stream)
+        for k in range(args.steps):
+            ev[k][0].record(stream)
+            _capi.check("snn_lif_fwd", L.snn_lif_fwd(px, ps, None, None, T, N, 0, ALPHA, THRESH, sp))
+            ev[k][1].record(stream)
+            _capi.check("snn_lif_bwd", L.snn_lif_bwd(px, pg, pgx, T, N, 0, ALPHA, THRESH, BETA, INTERVAL, None, 0, sp))
+            ev[k][2].record(stream)
+        e_end.record(stream)
+        barrier()
+    total_ms = e_start.elapsed_time(e_end)
+    fwd_ms = statistics.mean(e[0].elapsed_time(e[1]) for e in ev)
+    bwd_ms = statistics.mean(e[1].elapsed_time(e[2]) for e in ev)
+
+    if world > 1:
+        t = torch.tensor([total_ms, fwd_ms, bwd_ms], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        total_ms, fwd_ms, bwd_ms = (float(v) for v in t.tolist())
+    ms_per_step = total_ms / args.steps
+    value = gbps(N * world, ms_per_step / 1e3)
+
+    # ---- end to end through the host-buffer API: pinned host -> device -> kernels -> host ----
+    e2e = None
+    e2e_steps = max(2, min(5, args.steps))
+    for n_e2e in (N, N // 4, N // 16):
+        try:
+            hx = torch.empty((T, n_e2e), dtype=torch.float32).pin_memory()
+            hg = torch.empty((T, n_e2e), dtype=torch.float32).pin_memory()
+            hs = torch.empty((T, n_e2e), dtype=torch.float32).pin_memory()
+            hgx = torch.empty((T, n_e2e), dtype=torch.float32).pin_memory()
+        except RuntimeError:
+            continue
+        hx.copy_(x.view(T, N)[:, :n_e2e])
+        hg.copy_(g.view(T, N)[:, :n_e2e])
+        pipe = HostLifPipeline(T, n_e2e, torch.float32, chunk=1 << 22, lanes=3, device=dev)
+        pipe.run(hx, hg, hs, hgx, ALPHA, THRESH, BETA, INTERVAL)       # warm-up
+        barrier()
+        t0 = time.perf_counter()
+        for _ in range(e2e_steps):
+            pipe.run(hx, hg, hs, hgx, ALPHA, THRESH, BETA, INTERVAL)
+        torch.cuda.synchronize(dev)
+        dt = (time.perf_counter() - t0) / e2e_steps
+        if world > 1:
+            tt = torch.tensor([dt], device=dev, dtype=torch.float64)
+            dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+            dt = float(tt.item())
+        same = bool(torch.equal(hs[:, :4096].to(dev), spike.view(T, N)[:, :4096]))
+        e2e = {"value": round(gbps(n_e2e * world, dt), 2), "unit": "GB/s",
+               "h2d_bytes_per_step": pipe.h2d_bytes, "d2h_bytes_per_step": pipe.d2h_bytes,
+               "ms_per_step": round(dt * 1e3, 3), "neurons_per_gpu": n_e2e,
+               "launches_per_step": pipe.launches_per_run, "matches_device_run": same,
+               "how": "pinned host x,grad -> 3-stream chunked H2D / snn_lif_fwd / snn_lif_bwd / D2H of spike,grad_x"}
+        del hx, hg, hs, hgx, pipe
+        break
+
+    if rank == 0:
+        peak, peak_src = measured_peak()
+        bwd_gbs = BYTES_BWD * T * N / (bwd_ms / 1e3) / 1e9
+        fwd_gbs = BYTES_FWD * T * N / (fwd_ms / 1e3) / 1e9
+        traffic = (NCU_BWD_TRAFFIC_BYTES_PER_STEP * T * N) if NCU_BWD_TRAFFIC_BYTES_PER_STEP else None
+        out = {
+            "metric": "lif_fwd_bwd_hbm_gbps", "value": round(value, 2), "unit": "GB/s",
+            "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+            "ms_per_step": round(ms_per_step, 4), "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": WORKLOAD, "T": T, "neurons_per_gpu": N,
+                       "bytes_per_neuron_step": BYTES_FWD + BYTES_BWD,
+                       "l2": "inputs larger than L2 (8 GiB working set per step, no flush needed)",
+                       "parallelism": f"neuron-axis shards x{world}, no collective"},
+            "pct_of_measured_hbm_peak": round(100 * value / world / peak, 2),
+            "pct_of_nominal_8TBs": round(100 * value / world / NOMINAL_HBM_GBS, 2),
+            "kernels": {"lif_fwd_ms": round(fwd_ms, 4), "lif_fwd_gbs": round(fwd_gbs, 1),
+                        "lif_bwd_ms": round(bwd_ms, 4), "lif_bwd_gbs": round(bwd_gbs, 1)},
+            "roofline": {"bound": "hbm", "kernel": "snn::lif_bwd_kernel<float,4,8>",
+                         "achieved": round(bwd_gbs, 1), "peak": peak, "unit": "GB/s",
+                         "frac": round(bwd_gbs / peak, 4), "traffic": traffic,
+                         "algorithmic_bytes_per_launch": BYTES_BWD * T * N, "peak_source": peak_src},
+            "clocks": clocks.summary(),
+            "e2e": e2e,
+            "gpu_launches": 2 * args.steps,
+        }
+        if world == 1 and not args.no_cpu:
+            out["cpu_baseline"] = cpu_baseline_block()
+        print(json.dumps(out))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference_arm(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,114 @@
+/*
+ * snn_b200.h - C ABI of libsnn_b200.so: the LIF "fire" forward / BPTT backward hot path
+ * of liangling76/snn_gpu_training_bptt's `snnlib`, as hand-written sm_100a kernels.
+ *
+ * Conventions
+ *   - plain C types only; every buffer is DEVICE memory owned by the caller; nothing is
+ *     allocated, cached or freed by the library; outputs are written in full;
+ *   - tensors are time-major and contiguous: [T, N] with element (t, n) at t*N + n, where
+ *     N = B*C*H*W is the reference's per-time-step element count (its `BCHW`,
+ *     snnlib/cuda/snn_kernel_fp.cu:60-63); neurons are independent, so B and CHW need not
+ *     be passed separately;
+ *   - `stream` is a cudaStream_t passed as void* (NULL = the legacy default stream, which is
+ *     where the reference launches: snn_kernel_fp.cu:68);
+ *   - every entry point validates its arguments BEFORE launching and returns an
+ *     snn_status; on any non-zero status nothing was launched. The reference has no error
+ *     convention at all (no checks in snnlib/cuda/snn.cpp), so this is a strict superset;
+ *   - work is enqueued asynchronously; a launch failure reported by the runtime is
+ *     returned as SNN_ERR_CUDA (detail via snn_last_cuda_error()).
+ */
+#ifndef SNN_B200_H
+#define SNN_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum snn_status {
+    SNN_OK = 0,
+    SNN_ERR_NULL = 1,        /* a required pointer is NULL */
+    SNN_ERR_SHAPE = 2,       /* T < 1, N < 0, or a size that does not fit the kernels' index types */
+    SNN_ERR_DTYPE = 3,       /* dtype is not one of snn_dtype */
+    SNN_ERR_ALIGN = 4,       /* a pointer is not aligned to its element size */
+    SNN_ERR_UNSUPPORTED = 5, /* valid request this build cannot serve (e.g. spike words with T > 32) */
+    SNN_ERR_WORKSPACE = 6,   /* scratch buffer missing or too small */
+    SNN_ERR_CUDA = 7         /* the CUDA runtime reported an error at launch */
+} snn_status;
+
+/* Element type of the tensors in global memory. State is always carried in fp32
+ * (fp64 for SNN_F64), whatever the I/O type. */
+typedef enum snn_dtype {
+    SNN_F32 = 0,
+    SNN_BF16 = 1,
+    SNN_F16 = 2,
+    SNN_F64 = 3
+} snn_dtype;
+
+/* Library version (major*10000 + minor*100 + patch). */
+int snn_version(void);
+
+/* Human-readable name of a status code (static string). */
+const char *snn_status_string(int status);
+
+/* cudaError_t of the most recent SNN_ERR_CUDA on this host thread (0 if none). */
+int snn_last_cuda_error(void);
+
+/*
+ * LIF forward:  u_t = (alpha*u_{t-1})*(1 - s_{t-1}) + x_t ;  s_t = (u_t > thresh) ; u, s start at 0.
+ *
+ * Replaces `fire_s_fp(spatial, alpha, thresh) -> spike` (snnlib/cuda/snn.cpp:11-17 ->
+ * fire_s_fp_cuda, snnlib/cuda/snn_kernel_fp.cu:55-73, kernel :15-53), and, through the
+ * optional `mem` output, the membrane re-materialisation kernels fire_u_fp_kernel /
+ * fire_us_fp_kernel (snnlib/cuda/snn_kernel_bp.cu:15-93).
+ *
+ *   x      [T, N] dtype            input currents
+ *   spike  [T, N] dtype  or NULL   0/1 spikes
+ *   mem    [T, N] fp32 (fp64 for SNN_F64) or NULL   membrane potentials u_t
+ *   bits   [N] words or NULL       packed spikes: bit t of word n = s(t, n); word is uint8 for
+ *                                  T <= 8, uint16 for T <= 16, uint32 for T <= 32
+ *                                  (SNN_ERR_UNSUPPORTED beyond 32)
+ * At least one of spike / mem / bits must be given.
+ */
+int snn_lif_fwd(const void *x, void *spike, void *mem, void *bits, int64_t T, int64_t N,
+                int dtype, float alpha, float thresh, void *stream);
+
+/*
+ * Scratch bytes snn_lif_bwd needs for this (T, N, dtype): 0 while the time axis fits in
+ * registers (T <= 32), else T*N*sizeof(state type) for a stored membrane tensor.
+ * Returns a negative snn_status on invalid arguments.
+ */
+int64_t snn_lif_bwd_workspace_bytes(int64_t T, int64_t N, int dtype);
+
+/*
+ * LIF backward through time with the rectangular surrogate, walking t = T-1 .. 0:
+ *   inside = (u_t - thresh < interval) && (thresh - u_t < interval)
+ *   gs = inside ? g_t - (gu*alpha)*u_t : 0 ;  gu = gs*beta + (gu*alpha)*(u_t <= thresh) ;  grad_x_t = gu
+ *
+ * Replaces `fire_bp(spatial, grad_spike, alpha, thresh, beta, interval) -> grad_spatial`
+ * (snnlib/cuda/snn.cpp:270-279 -> fire_bp_cuda, snnlib/cuda/snn_kernel_bp.cu:141-168, which
+ * allocates a membrane tensor, runs fire_u_fp_kernel :15-52, then fire_bp_kernel :95-139).
+ * Here u_t is rebuilt in registers from x inside one kernel.
+ *
+ *   x, grad_spike  [T, N] dtype   saved input currents, upstream gradient w.r.t. the spikes
+ *   grad_x         [T, N] dtype   output
+ *   workspace      device scratch of at least snn_lif_bwd_workspace_bytes() bytes, 256-byte
+ *                  aligned; may be NULL when that is 0
+ */
+int snn_lif_bwd(const void *x, const void *grad_spike, void *grad_x, int64_t T, int64_t N,
+                int dtype, float alpha, float thresh, float beta, float interval,
+                void *workspace, size_t workspace_bytes, void *stream);
+
+/*
+ * Expand packed spike words (as written by snn_lif_fwd's `bits`) into a dense [T, N] 0/1
+ * tensor of `dtype`. No counterpart in the reference, which stores spikes densely.
+ */
+int snn_spike_unpack(const void *bits, void *spike, int64_t T, int64_t N, int dtype,
+                     void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SNN_B200_H */

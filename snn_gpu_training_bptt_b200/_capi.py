@@ -1,0 +1,151 @@
+"""ctypes binding of libsnn_b200.so (C ABI declared in include/snn_b200.h).
+
+There is exactly one backend. If the shared library has not been built, or a call returns
+a non-zero status, this module raises; it never falls back to another implementation.
+"""
+import ctypes
+import os
+
+import torch
+
+_PKG = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_PKG, "libsnn_b200.so")
+
+SNN_OK = 0
+DTYPE_CODE = {torch.float32: 0, torch.bfloat16: 1, torch.float16: 2, torch.float64: 3}
+STATE_DTYPE = {torch.float32: torch.float32, torch.bfloat16: torch.float32,
+               torch.float16: torch.float32, torch.float64: torch.float64}
+
+# every symbol include/snn_b200.h declares: (restype, argtypes)
+_vp, _i64, _f32, _int, _sz = (ctypes.c_void_p, ctypes.c_int64, ctypes.c_float, ctypes.c_int,
+                              ctypes.c_size_t)
+SIGNATURES = {
+    "snn_version": (_int, []),
+    "snn_status_string": (ctypes.c_char_p, [_int]),
+    "snn_last_cuda_error": (_int, []),
+    "snn_lif_fwd": (_int, [_vp, _vp, _vp, _vp, _i64, _i64, _int, _f32, _f32, _vp]),
+    "snn_lif_bwd_workspace_bytes": (_i64, [_i64, _i64, _int]),
+    "snn_lif_bwd": (_int, [_vp, _vp, _vp, _i64, _i64, _int, _f32, _f32, _f32, _f32, _vp, _sz, _vp]),
+    "snn_spike_unpack": (_int, [_vp, _vp, _i64, _i64, _int, _vp]),
+}
+
+
+class SnnError(RuntimeError):
+    """A C-ABI call returned a non-zero snn_status."""
+
+    def __init__(self, fn, status, detail):
+        super().__init__(f"{fn} failed: status {status} ({detail})")
+        self.status = status
+
+
+_lib = None
+
+
+def lib():
+    """Load libsnn_b200.so once; raise if it is missing (no fallback exists)."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise RuntimeError(
+                f"{LIB_PATH} is missing: build it with "
+                "`python -m snn_gpu_training_bptt_b200.build` (needs nvcc). "
+                "There is no CPU or PyTorch fallback for these ops.")
+        handle = ctypes.CDLL(LIB_PATH)
+        for name, (restype, argtypes) in SIGNATURES.items():
+            fn = getattr(handle, name)  # AttributeError if the symbol is not exported
+            fn.restype, fn.argtypes = restype, argtypes
+        _lib = handle
+    return _lib
+
+
+def check(fn_name, status):
+    if status != SNN_OK:
+        L = lib()
+        detail = L.snn_status_string(status).decode()
+        if status == 7:
+            detail += f", cudaError {L.snn_last_cuda_error()}"
+        raise SnnError(fn_name, status, detail)
+
+
+def _ptr(t):
+    return ctypes.c_void_p(t.data_ptr()) if t is not None else None
+
+
+def _stream(device):
+    return ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
+
+
+def _require_cuda(t, name):
+    if not isinstance(t, torch.Tensor):
+        raise TypeError(f"{name} must be a torch.Tensor")
+    if not t.is_cuda:
+        raise ValueError(f"{name} must be a CUDA tensor (this library has no CPU path)")
+    if t.dtype not in DTYPE_CODE:
+        raise TypeError(f"{name}: unsupported dtype {t.dtype}; use float32, bfloat16, float16 or float64")
+    if t.dim() < 2:
+        raise ValueError(f"{name} must be time-major [T, B, ...]")
+    if t.shape[0] < 1:
+        raise ValueError(f"{name} has an empty time axis")
+
+
+def bits_dtype(T):
+    if T > 32:
+        raise ValueError("packed spike words cover at most 32 time steps")
+    return torch.uint8 if T <= 8 else (torch.int16 if T <= 16 else torch.int32)
+
+
+def lif_fwd(x, alpha, thresh, want_spike=True, want_mem=False, want_bits=False):
+    """Run snn_lif_fwd on a [T, ...] CUDA tensor; returns (spike, mem, bits) with None for
+    outputs not requested. Launches on torch's current stream of x's device."""
+    _require_cuda(x, "spatial")
+    x = x.contiguous()
+    T = x.shape[0]
+    N = x.numel() // T
+    with torch.cuda.device(x.device):
+        spike = torch.empty_like(x) if want_spike else None
+        mem = torch.empty(x.shape, dtype=STATE_DTYPE[x.dtype], device=x.device) if want_mem else None
+        bits = torch.empty(x.shape[1:], dtype=bits_dtype(T), device=x.device) if want_bits else None
+        rc = lib().snn_lif_fwd(_ptr(x), _ptr(spike), _ptr(mem), _ptr(bits), T, N,
+                               DTYPE_CODE[x.dtype], float(alpha), float(thresh), _stream(x.device))
+    check("snn_lif_fwd", rc)
+    return spike, mem, bits
+
+
+def lif_bwd(x, grad_spike, alpha, thresh, beta, interval):
+    """Run snn_lif_bwd; returns grad_x shaped like x."""
+    _require_cuda(x, "spatial")
+    _require_cuda(grad_spike, "grad_spike")
+    if grad_spike.shape != x.shape:
+        raise ValueError(f"grad_spike shape {tuple(grad_spike.shape)} != spatial shape {tuple(x.shape)}")
+    if grad_spike.dtype != x.dtype or grad_spike.device != x.device:
+        raise TypeError("grad_spike must have spatial's dtype and device")
+    x = x.contiguous()
+    g = grad_spike.contiguous()
+    T = x.shape[0]
+    N = x.numel() // T
+    code = DTYPE_CODE[x.dtype]
+    with torch.cuda.device(x.device):
+        need = lib().snn_lif_bwd_workspace_bytes(T, N, code)
+        if need < 0:
+            check("snn_lif_bwd_workspace_bytes", -need)
+        ws = torch.empty(need, dtype=torch.uint8, device=x.device) if need > 0 else None
+        gx = torch.empty_like(x)
+        rc = lib().snn_lif_bwd(_ptr(x), _ptr(g), _ptr(gx), T, N, code, float(alpha), float(thresh),
+                               float(beta), float(interval), _ptr(ws), need, _stream(x.device))
+    check("snn_lif_bwd", rc)
+    return gx
+
+
+def spike_unpack(bits, T, dtype=torch.float32):
+    """Expand packed spike words [B, ...] into a dense [T, B, ...] 0/1 tensor."""
+    if not bits.is_cuda:
+        raise ValueError("bits must be a CUDA tensor")
+    if bits.dtype != bits_dtype(T):
+        raise TypeError(f"bits dtype {bits.dtype} does not match T={T}")
+    bits = bits.contiguous()
+    N = bits.numel()
+    with torch.cuda.device(bits.device):
+        out = torch.empty((T,) + tuple(bits.shape), dtype=dtype, device=bits.device)
+        rc = lib().snn_spike_unpack(_ptr(bits), _ptr(out), T, N, DTYPE_CODE[dtype], _stream(bits.device))
+    check("snn_spike_unpack", rc)
+    return out

@@ -1,0 +1,157 @@
+"""Generate the golden vectors under tests/golden/ from the REFERENCE's own gold ops.
+
+Run once, in a container where the reference checkout is mounted:
+
+    python tests/golden/make_golden.py [--ref /path/to/reference]
+
+It imports ``snnlib/example/gold_op.py`` of liangling76/snn_gpu_training_bptt (pure PyTorch,
+CPU) and records, for seeded inputs, the membrane potentials, spikes and input gradients
+that ``gold_fire`` (gold_op.py:34-44, surrogate gold_op.py:17-31) produces, plus the
+fire->fc / fc compositions of ``gold_op.BnFireFc`` (gold_op.py:118-150). The reference
+ships no stored vectors of its own: its test scripts (snnlib/example/test_fire.py,
+test_fire_fc.py, test_fc.py) print differences against these very functions, so their
+outputs are what pins parity. The committed ``*.npz`` files travel with the repository;
+the reference itself is not needed to run the tests.
+"""
+import argparse
+import hashlib
+import os
+import sys
+
+import numpy as np
+import torch
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def sha(a):
+    return hashlib.sha256(np.ascontiguousarray(a).tobytes()).hexdigest()
+
+
+def fire_case(gop, x, g):
+    """gold_fire forward, then backward with upstream gradient g applied to the spikes."""
+    gop.time_step = x.shape[0]
+    xr = x.clone().requires_grad_(True)
+    u, s = gop.gold_fire(xr)
+    s.backward(g)
+    return u.detach().numpy(), s.detach().numpy(), xr.grad.numpy()
+
+
+def ce_head_case(gop, x, labels):
+    """The reference test's own head (test_fire.py:24-46): time-mean -> CrossEntropy."""
+    gop.time_step = x.shape[0]
+    xr = x.clone().requires_grad_(True)
+    u, s = gop.gold_fire(xr)
+    out = s.view(s.shape[0], s.shape[1], -1).mean(dim=0)
+    loss = torch.nn.CrossEntropyLoss()(out, labels)
+    loss.backward()
+    return u.detach().numpy(), s.detach().numpy(), xr.grad.numpy(), out.detach().numpy(), float(loss.detach())
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--ref", default="/root/reference")
+    args = ap.parse_args()
+    sys.path.insert(0, os.path.join(args.ref, "snnlib", "example"))
+    import gold_op as gop  # the reference's module
+
+    torch.set_num_threads(1)
+    out = {}
+
+    # ---- 1. shapes of the reference's own test fixtures (test_utils.py:5-27), T = 6 -------
+    gen = torch.Generator().manual_seed(20240601)
+    labels = torch.tensor([1, 0])
+    for name, shape in (("ut_fc", (6, 2, 8)), ("ut_conv", (6, 2, 8, 8, 8))):
+        x = torch.randn(shape, generator=gen)
+        u, s, gx, head, loss = ce_head_case(gop, x, labels)
+        out[f"{name}_x"], out[f"{name}_u"], out[f"{name}_s"] = x.numpy(), u, s
+        out[f"{name}_gx_ce"], out[f"{name}_head"], out[f"{name}_loss"] = gx, head, np.float32(loss)
+        g = torch.randn(shape, generator=gen)
+        _, _, gx2 = fire_case(gop, x, g)
+        out[f"{name}_g"], out[f"{name}_gx"] = g.numpy(), gx2
+
+    # ---- 2. ragged neuron counts and several T, inputs N(0.5, 1), upstream N(0, 1) ---------
+    for T, N in ((1, 37), (2, 130), (4, 1003), (6, 515), (8, 4099), (16, 1021), (20, 259), (33, 65)):
+        gen = torch.Generator().manual_seed(1000 + T)
+        x = 0.5 + torch.randn((T, 1, N), generator=gen)
+        g = torch.randn((T, 1, N), generator=gen)
+        u, s, gx = fire_case(gop, x, g)
+        k = f"rag_T{T}_N{N}"
+        out[f"{k}_x"], out[f"{k}_g"] = x.numpy(), g.numpy()
+        out[f"{k}_u"], out[f"{k}_s"], out[f"{k}_gx"] = u, s, gx
+
+    # ---- 3. hand-placed edge values: threshold, window edges, resets, zeros, large ---------
+    th, iv = gop.thresh, gop.interval
+    cols = [
+        [th] * 8,                                     # u == thresh exactly: no spike (strict >)
+        [np.nextafter(np.float32(th), np.float32(1))] * 8,   # one ulp above: spike every step
+        [th + iv] * 8,                                # upper window edge (strict <): outside
+        [th - iv] * 8,                                # lower window edge: outside
+        [np.nextafter(np.float32(th + iv), np.float32(0))] * 8,
+        [np.nextafter(np.float32(th - iv), np.float32(1))] * 8,
+        [0.0] * 8,
+        [-0.0] * 8,
+        [1e30, -1e30, 1e-30, -1e-30, 3e38, -3e38, 1.0, -1.0],
+        [0.2, 0.2, 0.2, 0.2, 0.2, 0.2, 0.2, 0.2],     # slow integration to a spike
+        [1.0, 0.0, 0.0, 0.0, 1.0, 0.0, 0.0, 0.0],     # spike then hard reset
+        [-5.0, 1.5, -5.0, 1.5, -5.0, 1.5, -5.0, 1.5],
+        [0.24999999, 0.25000003, 0.75, -0.25, 0.7499999, -0.2499999, 0.5, 0.1],
+    ]
+    x = torch.tensor(np.array(cols, dtype=np.float32).T.copy()).reshape(8, 1, len(cols))
+    gen = torch.Generator().manual_seed(77)
+    g = torch.randn(x.shape, generator=gen)
+    u, s, gx = fire_case(gop, x, g)
+    out["edge_x"], out["edge_g"], out["edge_u"], out["edge_s"], out["edge_gx"] = (
+        x.numpy(), g.numpy(), u, s, gx)
+
+    # ---- 4. fire->fc and plain fc compositions (test_fire_fc.py, test_fc.py), T = 6 -------
+    gop.time_step = 6
+    for name, shape, cin in (("fc", (6, 2, 8), 8), ("conv", (6, 2, 8, 8, 8), 512)):
+        for fire in (True, False):
+            torch.manual_seed(4242 + cin + int(fire))
+            mod = gop.BnFireFc(cin, 8, fire=fire)
+            w = torch.randn(8, cin)
+            b = torch.randn(8)
+            mod.fc.weight = torch.nn.Parameter(w.clone())
+            mod.fc.bias = torch.nn.Parameter(b.clone())
+            x = torch.randn(shape)
+            xr = x.clone().requires_grad_(True)
+            y = mod(xr)
+            gy = torch.randn(y.shape)
+            y.backward(gy)
+            k = f"{'firefc' if fire else 'fc'}_{name}"
+            out[f"{k}_x"], out[f"{k}_w"], out[f"{k}_b"] = x.numpy(), w.numpy(), b.numpy()
+            out[f"{k}_y"], out[f"{k}_gy"] = y.detach().numpy(), gy.numpy()
+            out[f"{k}_gx"] = xr.grad.numpy()
+            out[f"{k}_gw"] = mod.fc.weight.grad.numpy()
+            out[f"{k}_gb"] = mod.fc.bias.grad.numpy()
+
+    np.savez_compressed(os.path.join(HERE, "lif_golden.npz"), **out)
+
+    # ---- 5. the full single-layer case: T=8, [32,128,16,16], seed 1234 ---------------------
+    # Too large to store; keep digests of inputs and outputs plus a strided sample.
+    torch.set_num_threads(os.cpu_count() or 1)
+    gen = torch.Generator().manual_seed(1234)
+    shape = (8, 32, 128, 16, 16)
+    x = 0.5 + torch.randn(shape, generator=gen)
+    g = torch.randn(shape, generator=gen)
+    u, s, gx = fire_case(gop, x, g)
+    stride = 4099
+    big = {
+        "shape": np.array(shape), "seed": np.array(1234), "stride": np.array(stride),
+        "x_sha": np.array(sha(x.numpy())), "g_sha": np.array(sha(g.numpy())),
+        "u_sha": np.array(sha(u)), "s_sha": np.array(sha(s)),
+        "gx_sha": np.array(sha(gx + 0.0)),   # "+ 0.0" folds -0.0 into +0.0 before hashing
+        "x_sample": x.numpy().reshape(-1)[::stride], "g_sample": g.numpy().reshape(-1)[::stride],
+        "u_sample": u.reshape(-1)[::stride], "s_sample": s.reshape(-1)[::stride],
+        "gx_sample": gx.reshape(-1)[::stride],
+        "spike_rate": np.array(s.mean(dtype=np.float64)),
+        "gx_abs_sum": np.array(np.abs(gx).sum(dtype=np.float64)),
+    }
+    np.savez_compressed(os.path.join(HERE, "lif_config1_digest.npz"), **big)
+    print("wrote", sorted(os.listdir(HERE)))
+    print("config-1 spike rate", float(big["spike_rate"]))
+
+
+if __name__ == "__main__":
+    main()

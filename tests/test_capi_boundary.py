@@ -1,0 +1,84 @@
+"""The C-ABI boundary, checked without a GPU: the library loads, exports every symbol that
+include/snn_b200.h declares, and validates arguments before it would launch anything."""
+import ctypes
+import os
+import re
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _declared_symbols():
+    text = open(os.path.join(ROOT, "include", "snn_b200.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(snn_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_header_declares_the_hot_path():
+    names = _declared_symbols()
+    for required in ("snn_lif_fwd", "snn_lif_bwd", "snn_lif_bwd_workspace_bytes", "snn_version"):
+        assert required in names
+
+
+def test_library_exports_every_declared_symbol(built_lib):
+    handle = ctypes.CDLL(built_lib)
+    for name in _declared_symbols():
+        assert hasattr(handle, name), f"{name} declared in snn_b200.h but not exported"
+
+
+def test_binding_table_matches_header(built_lib):
+    from snn_gpu_training_bptt_b200 import _capi
+    assert sorted(_capi.SIGNATURES) == _declared_symbols()
+    assert _capi.lib().snn_version() >= 100
+
+
+def test_argument_validation_needs_no_gpu(built_lib):
+    """Every bad call returns its status before any CUDA call is made."""
+    from snn_gpu_training_bptt_b200 import _capi
+    L = _capi.lib()
+    p = ctypes.c_void_p
+    fake, odd = p(0x1000), p(0x1002)
+    # forward
+    assert L.snn_lif_fwd(None, fake, None, None, 8, 16, 0, 0.25, 0.25, None) == 1        # NULL x
+    assert L.snn_lif_fwd(fake, None, None, None, 8, 16, 0, 0.25, 0.25, None) == 1        # no output
+    assert L.snn_lif_fwd(fake, fake, None, None, 0, 16, 0, 0.25, 0.25, None) == 2        # T < 1
+    assert L.snn_lif_fwd(fake, fake, None, None, 8, -1, 0, 0.25, 0.25, None) == 2        # N < 0
+    assert L.snn_lif_fwd(fake, fake, None, None, 8, 16, 9, 0.25, 0.25, None) == 3        # dtype
+    assert L.snn_lif_fwd(odd, fake, None, None, 8, 16, 0, 0.25, 0.25, None) == 4         # misaligned fp32
+    assert L.snn_lif_fwd(fake, None, None, fake, 33, 16, 0, 0.25, 0.25, None) == 5       # bits beyond 32 steps
+    assert L.snn_lif_fwd(fake, fake, None, None, 8, 0, 0, 0.25, 0.25, None) == 0         # empty: ok, nothing to do
+    # backward
+    assert L.snn_lif_bwd(fake, None, fake, 8, 16, 0, 0.25, 0.25, 1.0, 0.5, None, 0, None) == 1
+    assert L.snn_lif_bwd(fake, fake, fake, 8, 16, 7, 0.25, 0.25, 1.0, 0.5, None, 0, None) == 3
+    assert L.snn_lif_bwd(fake, fake, fake, 40, 16, 0, 0.25, 0.25, 1.0, 0.5, None, 0, None) == 6   # long T, no scratch
+    assert L.snn_lif_bwd(fake, fake, fake, 40, 16, 0, 0.25, 0.25, 1.0, 0.5, fake, 100, None) == 6  # scratch too small
+    assert L.snn_lif_bwd(fake, fake, fake, 8, 0, 0, 0.25, 0.25, 1.0, 0.5, None, 0, None) == 0
+    # workspace query
+    assert L.snn_lif_bwd_workspace_bytes(8, 1 << 26, 0) == 0
+    assert L.snn_lif_bwd_workspace_bytes(32, 1000, 1) == 0
+    assert L.snn_lif_bwd_workspace_bytes(33, 1000, 1) == 33 * 1000 * 4
+    assert L.snn_lif_bwd_workspace_bytes(64, 10, 3) == 64 * 10 * 8
+    assert L.snn_lif_bwd_workspace_bytes(0, 10, 0) == -2
+    # unpack
+    assert L.snn_spike_unpack(None, fake, 8, 16, 0, None) == 1
+    assert L.snn_spike_unpack(fake, fake, 40, 16, 0, None) == 5
+    assert L.snn_status_string(6).decode().startswith("workspace")
+
+
+def test_missing_library_fails_loudly(monkeypatch, tmp_path):
+    from snn_gpu_training_bptt_b200 import _capi
+    monkeypatch.setattr(_capi, "_lib", None)
+    monkeypatch.setattr(_capi, "LIB_PATH", str(tmp_path / "libsnn_b200.so"))
+    with pytest.raises(RuntimeError, match="no CPU or PyTorch fallback"):
+        _capi.lib()
+
+
+def test_cpu_tensors_are_rejected(built_lib):
+    import torch
+    from snn_gpu_training_bptt_b200 import snnlib
+    x = torch.zeros(4, 2, 8)
+    with pytest.raises(ValueError, match="CUDA"):
+        snnlib.fire_s_fp(x, 0.25, 0.25)
+    with pytest.raises(ValueError, match="CUDA"):
+        snnlib.fire_bp(x, x, 0.25, 0.25, 1.0, 0.5)
