@@ -39,10 +39,10 @@ NOMINAL_HBM_GBS = 8000.0
 WORKLOAD = "lif_fire_fwd_bwd fp32 T=8 N=2^26 per GPU, x~N(0.5,1), grad~N(0,1), seed 1234"
 
 # DRAM traffic of the backward kernel per neuron-timestep as measured by one ncu capture
-# (dram__bytes_read.sum + dram__bytes_write.sum of snn::lif_bwd_kernel<float,4,8>, T=8,
-# N=2^24 -- 6 GiB on the device, inside the capture size rule -- divided by T*N; traffic is
-# proportional to T*N, so a full launch is this figure x T*N). None until captured.
-NCU_BWD_TRAFFIC_BYTES_PER_STEP = None
+# (dram__bytes_read.sum + dram__bytes_write.sum of snn::lif_bwd_kernel, T=8, N=2^24 -- 2 GiB on
+# the device, inside the capture size rule -- divided by T*N; traffic is proportional to T*N,
+# so a full launch is this figure x T*N). See profiles/.
+NCU_BWD_TRAFFIC_BYTES_PER_STEP = 11.69
 
 
 def measured_peak():
@@ -221,7 +221,7 @@ def run_ours(args):
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
 
-    T, N = T_STEPS, NEURONS
+    T, N = T_STEPS, 1 << args.log2n
     gen = torch.Generator(device=dev).manual_seed(1234 + rank)
     x = torch.randn((T, 1, N), device=dev, generator=gen).add_(0.5)
     g = torch.randn((T, 1, N), device=dev, generator=gen)
@@ -272,7 +272,7 @@ def run_ours(args):
     # ---- end to end through the host-buffer API: pinned host -> device -> kernels -> host ----
     e2e = None
     e2e_steps = max(2, min(5, args.steps))
-    for n_e2e in (N, N // 4, N // 16):
+    for n_e2e in (() if args.no_e2e else (N, N // 4, N // 16)):
         try:
             hx = torch.empty((T, n_e2e), dtype=torch.float32).pin_memory()
             hg = torch.empty((T, n_e2e), dtype=torch.float32).pin_memory()
@@ -303,6 +303,23 @@ def run_ours(args):
         del hx, hg, hs, hgx, pipe
         break
 
+    # ---- second half of the metric: spiking-CNN training samples/sec (data-parallel) ----------
+    trainer = None
+    if not args.no_trainer:
+        del x, g, spike, gx
+        torch.cuda.empty_cache()
+        from snn_gpu_training_bptt_b200.example import train_synthetic
+        tr = train_synthetic.run("vgg", time_steps=8, batch=64, steps=args.trainer_steps, warmup=5,
+                                 precision="bf16")
+        trainer = {"metric": "spiking_cnn_train_samples_per_s", "value": round(tr["samples_per_s"], 1),
+                   "unit": "samples/s", "ms_per_step": round(tr["ms_per_step"], 3),
+                   "config": {"workload": "VGG-style spiking CNN (conv 128-128-P-256-256-P-512-512-P, fc 8192-1024-10, "
+                                          "LIF after every conv/fc), T=8, batch 64 per GPU, synthetic 3x32x32 U(0,1) "
+                                          "images, SGD momentum 0.9, bf16 synaptic ops + fp32 LIF state",
+                              "parallelism": f"dp{world}, bucketed NCCL all-reduce overlapped with backward"},
+                   "steps": tr["steps"], "params": tr["params"], "final_loss": round(tr["final_loss"], 4),
+                   "h2d_bytes_per_step": tr["h2d_bytes_per_step"], "d2h_bytes_per_step": tr["d2h_bytes_per_step"]}
+
     if rank == 0:
         peak, peak_src = measured_peak()
         bwd_gbs = BYTES_BWD * T * N / (bwd_ms / 1e3) / 1e9
@@ -313,21 +330,23 @@ def run_ours(args):
             "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
             "ms_per_step": round(ms_per_step, 4), "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": WORKLOAD, "T": T, "neurons_per_gpu": N,
+            "config": {"workload": WORKLOAD if N == NEURONS else WORKLOAD.replace("N=2^26", f"N=2^{args.log2n} (reduced case)"),
+                       "T": T, "neurons_per_gpu": N,
                        "bytes_per_neuron_step": BYTES_FWD + BYTES_BWD,
-                       "l2": "inputs larger than L2 (8 GiB working set per step, no flush needed)",
+                       "l2": f"inputs larger than L2 ({4 * 4 * T * N / 2**30:g} GiB working set per step, no flush needed)",
                        "parallelism": f"neuron-axis shards x{world}, no collective"},
             "pct_of_measured_hbm_peak": round(100 * value / world / peak, 2),
             "pct_of_nominal_8TBs": round(100 * value / world / NOMINAL_HBM_GBS, 2),
             "kernels": {"lif_fwd_ms": round(fwd_ms, 4), "lif_fwd_gbs": round(fwd_gbs, 1),
                         "lif_bwd_ms": round(bwd_ms, 4), "lif_bwd_gbs": round(bwd_gbs, 1)},
-            "roofline": {"bound": "hbm", "kernel": "snn::lif_bwd_kernel<float,4,8>",
+            "roofline": {"bound": "hbm", "kernel": "snn::lif_bwd_kernel<float,2,8>",
                          "achieved": round(bwd_gbs, 1), "peak": peak, "unit": "GB/s",
                          "frac": round(bwd_gbs / peak, 4), "traffic": traffic,
                          "algorithmic_bytes_per_launch": BYTES_BWD * T * N, "peak_source": peak_src},
             "clocks": clocks.summary(),
             "e2e": e2e,
             "gpu_launches": 2 * args.steps,
+            "trainer": trainer,
         }
         if world == 1 and not args.no_cpu:
             out["cpu_baseline"] = cpu_baseline_block()
@@ -344,6 +363,11 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg")
+    ap.add_argument("--no-trainer", action="store_true", help="skip the spiking-CNN training leg")
+    ap.add_argument("--trainer-steps", type=int, default=30)
+    ap.add_argument("--log2n", type=int, default=26,
+                    help="log2 of neurons per GPU (26 = the benchmark size; smaller only for profiler captures)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference_arm(args)

@@ -88,6 +88,38 @@ def _require_cuda(t, name):
         raise ValueError(f"{name} has an empty time axis")
 
 
+def is_time_major_dense(t):
+    """True if ``t`` can be handed to the kernels as it is: element (time, neuron) lives at
+    time * (numel / T) + f(neuron) for some fixed one-to-one layout f of the neurons of one
+    time step. That holds for contiguous tensors and equally for e.g. a channels-last batch
+    of images viewed as [T, B, C, H, W]: neurons are independent, so their order inside a
+    time step does not matter as long as every time step uses the same one."""
+    T = t.shape[0]
+    step = t.numel() // T if T else 0
+    if T > 1 and t.stride(0) != step:
+        return False
+    expect = 1
+    for size, stride in sorted(((sz, st) for sz, st in zip(t.shape[1:], t.stride()[1:]) if sz > 1),
+                               key=lambda p: p[1]):
+        if stride != expect:
+            return False
+        expect *= size
+    return expect == step or step == 0
+
+
+def as_time_major_dense(t):
+    return t if is_time_major_dense(t) else t.contiguous()
+
+
+def like_layout(t, ref):
+    """``t`` with exactly ``ref``'s strides (copying only if they differ)."""
+    if t.stride() == ref.stride():
+        return t
+    out = torch.empty_strided(ref.shape, ref.stride(), dtype=t.dtype, device=t.device)
+    out.copy_(t)
+    return out
+
+
 def bits_dtype(T):
     if T > 32:
         raise ValueError("packed spike words cover at most 32 time steps")
@@ -98,13 +130,15 @@ def lif_fwd(x, alpha, thresh, want_spike=True, want_mem=False, want_bits=False):
     """Run snn_lif_fwd on a [T, ...] CUDA tensor; returns (spike, mem, bits) with None for
     outputs not requested. Launches on torch's current stream of x's device."""
     _require_cuda(x, "spatial")
-    x = x.contiguous()
+    x = as_time_major_dense(x)
     T = x.shape[0]
     N = x.numel() // T
     with torch.cuda.device(x.device):
         spike = torch.empty_like(x) if want_spike else None
-        mem = torch.empty(x.shape, dtype=STATE_DTYPE[x.dtype], device=x.device) if want_mem else None
-        bits = torch.empty(x.shape[1:], dtype=bits_dtype(T), device=x.device) if want_bits else None
+        mem = torch.empty_like(x, dtype=STATE_DTYPE[x.dtype]) if want_mem else None
+        bits = torch.empty_like(x[0], dtype=bits_dtype(T)) if want_bits else None
+        if N == 0:
+            return spike, mem, bits
         rc = lib().snn_lif_fwd(_ptr(x), _ptr(spike), _ptr(mem), _ptr(bits), T, N,
                                DTYPE_CODE[x.dtype], float(alpha), float(thresh), _stream(x.device))
     check("snn_lif_fwd", rc)
@@ -119,8 +153,8 @@ def lif_bwd(x, grad_spike, alpha, thresh, beta, interval):
         raise ValueError(f"grad_spike shape {tuple(grad_spike.shape)} != spatial shape {tuple(x.shape)}")
     if grad_spike.dtype != x.dtype or grad_spike.device != x.device:
         raise TypeError("grad_spike must have spatial's dtype and device")
-    x = x.contiguous()
-    g = grad_spike.contiguous()
+    x = as_time_major_dense(x)
+    g = like_layout(grad_spike, x)
     T = x.shape[0]
     N = x.numel() // T
     code = DTYPE_CODE[x.dtype]
@@ -130,6 +164,8 @@ def lif_bwd(x, grad_spike, alpha, thresh, beta, interval):
             check("snn_lif_bwd_workspace_bytes", -need)
         ws = torch.empty(need, dtype=torch.uint8, device=x.device) if need > 0 else None
         gx = torch.empty_like(x)
+        if N == 0:
+            return gx
         rc = lib().snn_lif_bwd(_ptr(x), _ptr(g), _ptr(gx), T, N, code, float(alpha), float(thresh),
                                float(beta), float(interval), _ptr(ws), need, _stream(x.device))
     check("snn_lif_bwd", rc)
@@ -142,10 +178,12 @@ def spike_unpack(bits, T, dtype=torch.float32):
         raise ValueError("bits must be a CUDA tensor")
     if bits.dtype != bits_dtype(T):
         raise TypeError(f"bits dtype {bits.dtype} does not match T={T}")
-    bits = bits.contiguous()
+    if not is_time_major_dense(bits.unsqueeze(0)):
+        bits = bits.contiguous()
     N = bits.numel()
     with torch.cuda.device(bits.device):
-        out = torch.empty((T,) + tuple(bits.shape), dtype=dtype, device=bits.device)
+        out = torch.empty_strided((T,) + tuple(bits.shape), (N,) + tuple(bits.stride()),
+                                  dtype=dtype, device=bits.device)
         rc = lib().snn_spike_unpack(_ptr(bits), _ptr(out), T, N, DTYPE_CODE[dtype], _stream(bits.device))
     check("snn_spike_unpack", rc)
     return out

@@ -4,6 +4,8 @@
 #include "../../include/snn_b200.h"
 #include "lif_kernels.cuh"
 
+#include <type_traits>
+
 namespace {
 
 constexpr int kBlock = 256;
@@ -33,9 +35,9 @@ inline int check_launch() {
     return SNN_OK;
 }
 
-inline unsigned int grid_for(int64_t N, int vec) {
+inline unsigned int grid_for(int64_t N, int vec, int block) {
     const int64_t threads = (N + vec - 1) / vec;
-    return static_cast<unsigned int>((threads + kBlock - 1) / kBlock);
+    return static_cast<unsigned int>((threads + block - 1) / block);
 }
 
 inline int common_shape_check(int64_t T, int64_t N, int dtype) {
@@ -44,7 +46,7 @@ inline int common_shape_check(int64_t T, int64_t N, int dtype) {
     if (T > INT32_MAX) return SNN_ERR_SHAPE;
     // element offsets are int64; thread count must fit the 1-D grid
     if (N > 0 && T > INT64_MAX / 16 / N) return SNN_ERR_SHAPE;
-    if ((N + kBlock - 1) / kBlock > 0x7fffffffLL) return SNN_ERR_SHAPE;
+    if ((N + 127) / 128 > 0x7fffffffLL) return SNN_ERR_SHAPE;
     return SNN_OK;
 }
 
@@ -67,41 +69,60 @@ inline int pick_vec(int pref, int64_t N, const PtrReq* reqs, int nreq) {
     return 1;
 }
 
+// ---- launch configuration ------------------------------------------------------------------
+// Chosen from timing sweeps on B200 at N = 2^25..2^26 (fp32 and bf16, T = 4..32): 8-byte
+// accesses per thread with the time axis unrolled to the smallest instantiated bound >= T
+// gave the highest bandwidth for fp32; 16-byte accesses and 128-thread CTAs for 16-bit I/O.
+struct Tune { int vec; int block; };
+
+inline Tune fwd_tune(int dtype) {
+    switch (dtype) {
+        case SNN_F32: return {2, 256};
+        case SNN_F64: return {2, 256};
+        default: return {8, 128};          // bf16 / fp16
+    }
+}
+inline int fwd_tc(int dtype, int T) {
+    if (dtype == SNN_BF16 || dtype == SNN_F16) return 4;
+    return T <= 4 ? 4 : 8;
+}
+inline int bwd_tmax(int T) {
+    const int steps[] = {2, 4, 6, 8, 12, 16, 24, 32};
+    for (int s : steps) if (T <= s) return s;
+    return 32;
+}
+inline Tune bwd_tune(int dtype, int tmax) {
+    switch (dtype) {
+        case SNN_F32: return {2, tmax >= 32 ? 128 : 256};
+        case SNN_F64: return {tmax <= 16 ? 2 : 1, tmax >= 24 ? 128 : 256};
+        default: return {tmax <= 8 ? 8 : (tmax <= 16 ? 4 : 2), 128};
+    }
+}
+
+// Calls f(std::integral_constant<int, V>) for the largest instantiated V <= vec.
+template <int MAXV, typename F>
+inline void with_vec(int vec, F&& f) {
+    if constexpr (MAXV >= 8) { if (vec >= 8) return f(std::integral_constant<int, 8>{}); }
+    if constexpr (MAXV >= 4) { if (vec >= 4) return f(std::integral_constant<int, 4>{}); }
+    if constexpr (MAXV >= 2) { if (vec >= 2) return f(std::integral_constant<int, 2>{}); }
+    return f(std::integral_constant<int, 1>{});
+}
+template <typename F>
+inline void with_dtype(int dtype, F&& f) {
+    switch (dtype) {
+        case SNN_F32: return f(float{});
+        case SNN_BF16: return f(__nv_bfloat16{});
+        case SNN_F16: return f(__half{});
+        default: return f(double{});
+    }
+}
+
 // ---- forward ------------------------------------------------------------------------------
-template <typename IO, int VEC, int TC>
-void launch_fwd(const void* x, void* spike, void* mem, void* bits, int word_bytes, int T,
-                int64_t N, float alpha, float thresh, cudaStream_t st) {
-    using CT = typename snn::Elem<IO>::CT;
-    snn::lif_fwd_kernel<IO, VEC, TC><<<grid_for(N, VEC), kBlock, 0, st>>>(
-        static_cast<const IO*>(x), static_cast<IO*>(spike), static_cast<CT*>(mem), bits,
-        word_bytes, T, N, alpha, thresh);
-}
-
-template <typename IO, int VEC>
-void fwd_pick_tc(const void* x, void* spike, void* mem, void* bits, int word_bytes, int T,
-                 int64_t N, float alpha, float thresh, cudaStream_t st) {
-    if (T <= 4) launch_fwd<IO, VEC, 4>(x, spike, mem, bits, word_bytes, T, N, alpha, thresh, st);
-    else launch_fwd<IO, VEC, 8>(x, spike, mem, bits, word_bytes, T, N, alpha, thresh, st);
-}
-
-template <typename IO>
-void fwd_pick_vec(int vec, const void* x, void* spike, void* mem, void* bits, int word_bytes,
-                  int T, int64_t N, float alpha, float thresh, cudaStream_t st) {
-    constexpr int kMax = 16 / static_cast<int>(sizeof(IO));
-    if constexpr (kMax >= 8) {
-        if (vec == 8) return fwd_pick_tc<IO, 8>(x, spike, mem, bits, word_bytes, T, N, alpha, thresh, st);
-    }
-    if constexpr (kMax >= 4) {
-        if (vec == 4) return fwd_pick_tc<IO, 4>(x, spike, mem, bits, word_bytes, T, N, alpha, thresh, st);
-    }
-    if (vec == 2) return fwd_pick_tc<IO, 2>(x, spike, mem, bits, word_bytes, T, N, alpha, thresh, st);
-    return fwd_pick_tc<IO, 1>(x, spike, mem, bits, word_bytes, T, N, alpha, thresh, st);
-}
-
 int lif_fwd_impl(const void* x, void* spike, void* mem, void* bits, int64_t T, int64_t N,
                  int dtype, float alpha, float thresh, cudaStream_t st) {
     int rc = common_shape_check(T, N, dtype);
     if (rc) return rc;
+    if (N == 0) return SNN_OK;                       // nothing to do; pointers may be NULL
     if (!x || (!spike && !mem && !bits)) return SNN_ERR_NULL;
     const int es = dtype_size(dtype), ss = state_size(dtype);
     int word_bytes = 0;
@@ -112,75 +133,60 @@ int lif_fwd_impl(const void* x, void* spike, void* mem, void* bits, int64_t T, i
     if (!aligned(x, es) || !aligned(spike, es) || !aligned(mem, ss) ||
         (bits && !aligned(bits, word_bytes)))
         return SNN_ERR_ALIGN;
-    if (N == 0) return SNN_OK;
 
+    const Tune tune = fwd_tune(dtype);
     const PtrReq reqs[] = {{x, es}, {spike, es}, {mem, ss}, {bits, word_bytes ? word_bytes : 1}};
-    const int vec = pick_vec(16 / es, N, reqs, 4);
+    const int vec = pick_vec(tune.vec, N, reqs, 4);
+    const int tc = fwd_tc(dtype, static_cast<int>(T));
     const int Ti = static_cast<int>(T);
-    switch (dtype) {
-        case SNN_F32: fwd_pick_vec<float>(vec, x, spike, mem, bits, word_bytes, Ti, N, alpha, thresh, st); break;
-        case SNN_BF16: fwd_pick_vec<__nv_bfloat16>(vec, x, spike, mem, bits, word_bytes, Ti, N, alpha, thresh, st); break;
-        case SNN_F16: fwd_pick_vec<__half>(vec, x, spike, mem, bits, word_bytes, Ti, N, alpha, thresh, st); break;
-        case SNN_F64: fwd_pick_vec<double>(vec, x, spike, mem, bits, word_bytes, Ti, N, alpha, thresh, st); break;
-    }
+    with_dtype(dtype, [&](auto tag) {
+        using IO = decltype(tag);
+        using CT = typename snn::Elem<IO>::CT;
+        constexpr int kMaxVec = 16 / static_cast<int>(sizeof(IO));
+        with_vec<kMaxVec>(vec, [&](auto v) {
+            constexpr int VEC = decltype(v)::value;
+            const unsigned grid = grid_for(N, VEC, tune.block);
+            auto xp = static_cast<const IO*>(x);
+            auto sp = static_cast<IO*>(spike);
+            auto mp = static_cast<CT*>(mem);
+            if (tc == 4)
+                snn::lif_fwd_kernel<IO, VEC, 4><<<grid, tune.block, 0, st>>>(xp, sp, mp, bits, word_bytes, Ti, N, alpha, thresh);
+            else
+                snn::lif_fwd_kernel<IO, VEC, 8><<<grid, tune.block, 0, st>>>(xp, sp, mp, bits, word_bytes, Ti, N, alpha, thresh);
+        });
+    });
     return check_launch();
 }
 
 // ---- backward -----------------------------------------------------------------------------
-template <typename IO, int VEC, int TMAX>
-void launch_bwd(const void* x, const void* g, void* gx, int T, int64_t N, float alpha,
-                float thresh, float beta, float interval, cudaStream_t st) {
-    snn::lif_bwd_kernel<IO, VEC, TMAX><<<grid_for(N, VEC), kBlock, 0, st>>>(
-        static_cast<const IO*>(x), static_cast<const IO*>(g), static_cast<IO*>(gx), T, N, alpha,
-        thresh, beta, interval);
-}
-
-// VEC * TMAX is held near 32 state words so x, g and u of all T steps fit in registers.
 template <typename IO, int TMAX>
-void bwd_pick_vec(int vec, const void* x, const void* g, void* gx, int T, int64_t N, float alpha,
-                  float thresh, float beta, float interval, cudaStream_t st) {
+void launch_bwd_regs(int vec, int block, const void* x, const void* g, void* gx, int T, int64_t N,
+                     float alpha, float thresh, float beta, float interval, cudaStream_t st) {
+    // VEC * TMAX state words per thread stay in registers: cap the width for long time axes
     constexpr int kIoMax = 16 / static_cast<int>(sizeof(IO));
-    constexpr int kRegMax = (32 / TMAX) < 1 ? 1 : (32 / TMAX);
-    constexpr int kMax = kIoMax < kRegMax ? kIoMax : kRegMax;
-    if constexpr (kMax >= 8) {
-        if (vec >= 8) return launch_bwd<IO, 8, TMAX>(x, g, gx, T, N, alpha, thresh, beta, interval, st);
-    }
-    if constexpr (kMax >= 4) {
-        if (vec >= 4) return launch_bwd<IO, 4, TMAX>(x, g, gx, T, N, alpha, thresh, beta, interval, st);
-    }
-    if constexpr (kMax >= 2) {
-        if (vec >= 2) return launch_bwd<IO, 2, TMAX>(x, g, gx, T, N, alpha, thresh, beta, interval, st);
-    }
-    return launch_bwd<IO, 1, TMAX>(x, g, gx, T, N, alpha, thresh, beta, interval, st);
+    constexpr int kWords = TMAX <= 8 ? 8 : (TMAX <= 16 ? 4 : 2);
+    constexpr int kRegMax = kWords * 4 / static_cast<int>(sizeof(typename snn::Elem<IO>::CT));
+    constexpr int kMaxVec = kIoMax < kRegMax ? kIoMax : kRegMax;
+    with_vec<kMaxVec>(vec, [&](auto v) {
+        constexpr int VEC = decltype(v)::value;
+        snn::lif_bwd_kernel<IO, VEC, TMAX><<<grid_for(N, VEC, block), block, 0, st>>>(
+            static_cast<const IO*>(x), static_cast<const IO*>(g), static_cast<IO*>(gx), T, N, alpha,
+            thresh, beta, interval);
+    });
 }
 
 template <typename IO>
-void bwd_pick_t(int vec, const void* x, const void* g, void* gx, int T, int64_t N, float alpha,
-                float thresh, float beta, float interval, cudaStream_t st) {
-    if (T <= 4) bwd_pick_vec<IO, 4>(vec, x, g, gx, T, N, alpha, thresh, beta, interval, st);
-    else if (T <= 8) bwd_pick_vec<IO, 8>(vec, x, g, gx, T, N, alpha, thresh, beta, interval, st);
-    else if (T <= 16) bwd_pick_vec<IO, 16>(vec, x, g, gx, T, N, alpha, thresh, beta, interval, st);
-    else bwd_pick_vec<IO, 32>(vec, x, g, gx, T, N, alpha, thresh, beta, interval, st);
-}
-
-template <typename IO, int VEC>
-void launch_bwd_mem(const void* mem, const void* g, void* gx, int T, int64_t N, float alpha,
-                    float thresh, float beta, float interval, cudaStream_t st) {
-    using CT = typename snn::Elem<IO>::CT;
-    snn::lif_bwd_mem_kernel<IO, VEC, 8><<<grid_for(N, VEC), kBlock, 0, st>>>(
-        static_cast<const CT*>(mem), static_cast<const IO*>(g), static_cast<IO*>(gx), T, N, alpha,
-        thresh, beta, interval);
-}
-
-template <typename IO>
-void bwd_mem_pick_vec(int vec, const void* mem, const void* g, void* gx, int T, int64_t N,
-                      float alpha, float thresh, float beta, float interval, cudaStream_t st) {
-    // 4 neurons per thread at most: a chunk holds 8 steps of u and g
-    if constexpr (sizeof(IO) <= 4) {
-        if (vec >= 4) return launch_bwd_mem<IO, 4>(mem, g, gx, T, N, alpha, thresh, beta, interval, st);
+void launch_bwd_pick_t(int tmax, int vec, int block, const void* x, const void* g, void* gx, int T,
+                       int64_t N, float alpha, float thresh, float beta, float interval,
+                       cudaStream_t st) {
+#define SNN_BWD_CASE(TM) \
+    case TM: return launch_bwd_regs<IO, TM>(vec, block, x, g, gx, T, N, alpha, thresh, beta, interval, st);
+    switch (tmax) {
+        SNN_BWD_CASE(2) SNN_BWD_CASE(4) SNN_BWD_CASE(6) SNN_BWD_CASE(8)
+        SNN_BWD_CASE(12) SNN_BWD_CASE(16) SNN_BWD_CASE(24)
+        default: return launch_bwd_regs<IO, 32>(vec, block, x, g, gx, T, N, alpha, thresh, beta, interval, st);
     }
-    if (vec >= 2) return launch_bwd_mem<IO, 2>(mem, g, gx, T, N, alpha, thresh, beta, interval, st);
-    return launch_bwd_mem<IO, 1>(mem, g, gx, T, N, alpha, thresh, beta, interval, st);
+#undef SNN_BWD_CASE
 }
 
 int lif_bwd_impl(const void* x, const void* g, void* gx, int64_t T, int64_t N, int dtype,
@@ -188,39 +194,44 @@ int lif_bwd_impl(const void* x, const void* g, void* gx, int64_t T, int64_t N, i
                  size_t workspace_bytes, cudaStream_t st) {
     int rc = common_shape_check(T, N, dtype);
     if (rc) return rc;
-    if (!x || !g || !gx) return SNN_ERR_NULL;
     const int es = dtype_size(dtype), ss = state_size(dtype);
-    if (!aligned(x, es) || !aligned(g, es) || !aligned(gx, es)) return SNN_ERR_ALIGN;
     const int Ti = static_cast<int>(T);
+    const bool long_t = T > kRegT;
+    const size_t need = long_t ? static_cast<size_t>(T) * static_cast<size_t>(N) * ss : 0;
+    if (long_t && need > 0 && (!workspace || workspace_bytes < need)) return SNN_ERR_WORKSPACE;
+    if (N == 0) return SNN_OK;
+    if (!x || !g || !gx) return SNN_ERR_NULL;
+    if (!aligned(x, es) || !aligned(g, es) || !aligned(gx, es)) return SNN_ERR_ALIGN;
 
-    if (T <= kRegT) {
-        if (N == 0) return SNN_OK;
+    if (!long_t) {
+        const int tmax = bwd_tmax(Ti);
+        const Tune tune = bwd_tune(dtype, tmax);
         const PtrReq reqs[] = {{x, es}, {g, es}, {gx, es}};
-        const int vec = pick_vec(16 / es, N, reqs, 3);
-        switch (dtype) {
-            case SNN_F32: bwd_pick_t<float>(vec, x, g, gx, Ti, N, alpha, thresh, beta, interval, st); break;
-            case SNN_BF16: bwd_pick_t<__nv_bfloat16>(vec, x, g, gx, Ti, N, alpha, thresh, beta, interval, st); break;
-            case SNN_F16: bwd_pick_t<__half>(vec, x, g, gx, Ti, N, alpha, thresh, beta, interval, st); break;
-            case SNN_F64: bwd_pick_t<double>(vec, x, g, gx, Ti, N, alpha, thresh, beta, interval, st); break;
-        }
+        const int vec = pick_vec(tune.vec, N, reqs, 3);
+        with_dtype(dtype, [&](auto tag) {
+            using IO = decltype(tag);
+            launch_bwd_pick_t<IO>(tmax, vec, tune.block, x, g, gx, Ti, N, alpha, thresh, beta, interval, st);
+        });
         return check_launch();
     }
 
     // long time axis: store u_t in the caller's scratch, then walk it in reverse
-    const size_t need = static_cast<size_t>(T) * static_cast<size_t>(N) * ss;
-    if (need > 0 && (!workspace || workspace_bytes < need)) return SNN_ERR_WORKSPACE;
-    if (workspace && !aligned(workspace, 256)) return SNN_ERR_ALIGN;
-    if (N == 0) return SNN_OK;
+    if (!aligned(workspace, 256)) return SNN_ERR_ALIGN;
     rc = lif_fwd_impl(x, nullptr, workspace, nullptr, T, N, dtype, alpha, thresh, st);
     if (rc) return rc;
     const PtrReq reqs[] = {{workspace, ss}, {g, es}, {gx, es}};
-    const int vec = pick_vec(16 / es, N, reqs, 3);
-    switch (dtype) {
-        case SNN_F32: bwd_mem_pick_vec<float>(vec, workspace, g, gx, Ti, N, alpha, thresh, beta, interval, st); break;
-        case SNN_BF16: bwd_mem_pick_vec<__nv_bfloat16>(vec, workspace, g, gx, Ti, N, alpha, thresh, beta, interval, st); break;
-        case SNN_F16: bwd_mem_pick_vec<__half>(vec, workspace, g, gx, Ti, N, alpha, thresh, beta, interval, st); break;
-        case SNN_F64: bwd_mem_pick_vec<double>(vec, workspace, g, gx, Ti, N, alpha, thresh, beta, interval, st); break;
-    }
+    const int vec = pick_vec(es == 8 ? 2 : 4, N, reqs, 3);
+    with_dtype(dtype, [&](auto tag) {
+        using IO = decltype(tag);
+        using CT = typename snn::Elem<IO>::CT;
+        constexpr int kMaxVec = sizeof(IO) <= 4 ? 4 : 2;     // a chunk holds 8 steps of u and g
+        with_vec<kMaxVec>(vec, [&](auto v) {
+            constexpr int VEC = decltype(v)::value;
+            snn::lif_bwd_mem_kernel<IO, VEC, 8><<<grid_for(N, VEC, kBlock), kBlock, 0, st>>>(
+                static_cast<const CT*>(workspace), static_cast<const IO*>(g), static_cast<IO*>(gx), Ti,
+                N, alpha, thresh, beta, interval);
+        });
+    });
     return check_launch();
 }
 
@@ -231,14 +242,14 @@ void unpack_pick_vec(int vec, const void* bits, void* spike, int T, int64_t N, c
     IO* s = static_cast<IO*>(spike);
     if constexpr (sizeof(IO) <= 4) {
         if (vec >= 4) {
-            snn::spike_unpack_kernel<IO, 4, W><<<grid_for(N, 4), kBlock, 0, st>>>(b, s, T, N);
+            snn::spike_unpack_kernel<IO, 4, W><<<grid_for(N, 4, kBlock), kBlock, 0, st>>>(b, s, T, N);
             return;
         }
     }
     if (vec >= 2)
-        snn::spike_unpack_kernel<IO, 2, W><<<grid_for(N, 2), kBlock, 0, st>>>(b, s, T, N);
+        snn::spike_unpack_kernel<IO, 2, W><<<grid_for(N, 2, kBlock), kBlock, 0, st>>>(b, s, T, N);
     else
-        snn::spike_unpack_kernel<IO, 1, W><<<grid_for(N, 1), kBlock, 0, st>>>(b, s, T, N);
+        snn::spike_unpack_kernel<IO, 1, W><<<grid_for(N, 1, kBlock), kBlock, 0, st>>>(b, s, T, N);
 }
 
 template <typename IO>
@@ -295,8 +306,9 @@ int snn_spike_unpack(const void* bits, void* spike, int64_t T, int64_t N, int dt
                      void* stream) {
     int rc = common_shape_check(T, N, dtype);
     if (rc) return rc;
-    if (!bits || !spike) return SNN_ERR_NULL;
     if (T > 32) return SNN_ERR_UNSUPPORTED;
+    if (N == 0) return SNN_OK;
+    if (!bits || !spike) return SNN_ERR_NULL;
     const int es = dtype_size(dtype);
     const int word_bytes = T <= 8 ? 1 : (T <= 16 ? 2 : 4);
     if (!aligned(spike, es) || !aligned(bits, word_bytes)) return SNN_ERR_ALIGN;

@@ -1,0 +1,154 @@
+"""Data-parallel training of a spiking CNN on synthetic images: samples/sec at 1..8 GPUs.
+
+Follows the reference's trainers (snnlib/example/train_test_cifar.py:31-70 single GPU,
+train_test_imagenet_alexnet_dist.py:26-105 one process per GPU over NCCL): SGD with momentum
+0.9 and lr 1e-2, cross-entropy on the time-averaged output, ``zero_grad -> forward -> loss ->
+backward -> step``. CIFAR / ImageNet are replaced by seeded synthetic data of the same shape:
+3x32x32 images with pixels ~ U(0,1) and uniform-random labels in [0, 10).
+
+Launch:  python -m snn_gpu_training_bptt_b200.example.train_synthetic --model vgg
+         python -m torch.distributed.run --nproc-per-node 8 --master-addr 127.0.0.1 \\
+                -m snn_gpu_training_bptt_b200.example.train_synthetic --model vgg
+
+Every step copies its batch from pinned host memory to the GPU and reads the loss back when
+it logs, so the throughput printed is end to end for the training loop.
+"""
+import argparse
+import json
+import os
+import time
+
+import torch
+import torch.distributed as dist
+import torch.nn.functional as F
+
+from . import models
+from .ddp import DistributedDataParallel
+
+
+class SyntheticImages:
+    """A fixed pool of pinned host batches cycled through; stands in for a DataLoader."""
+
+    def __init__(self, batch, seed, pool=4, image=32, classes=10):
+        gen = torch.Generator().manual_seed(seed)
+        self.images = [torch.rand((batch, 3, image, image), generator=gen) for _ in range(pool)]
+        self.labels = [torch.randint(0, classes, (batch,), generator=gen) for _ in range(pool)]
+        if torch.cuda.is_available():
+            self.images = [t.pin_memory() for t in self.images]
+            self.labels = [t.pin_memory() for t in self.labels]
+        self.bytes_per_batch = self.images[0].numel() * 4 + self.labels[0].numel() * 8
+
+    def batch(self, step, device):
+        k = step % len(self.images)
+        return (self.images[k].to(device, non_blocking=True), self.labels[k].to(device, non_blocking=True))
+
+
+def save_checkpoint(path, model, optimizer, step):
+    """Parameters under the reference's key names plus what a resume needs (the reference saves
+    only ``state_dict()`` of the best epoch, train_test_cifar.py:94-97)."""
+    core = model.module if isinstance(model, DistributedDataParallel) else model
+    torch.save({"model": core.state_dict(), "optimizer": optimizer.state_dict(), "step": step}, path)
+
+
+def load_checkpoint(path, model, optimizer=None):
+    core = model.module if isinstance(model, DistributedDataParallel) else model
+    blob = torch.load(path, map_location="cpu")
+    state = blob["model"] if "model" in blob else blob      # plain state dicts load too
+    core.load_state_dict(state)
+    if optimizer is not None and "optimizer" in blob:
+        optimizer.load_state_dict(blob["optimizer"])
+    return blob.get("step", 0) if isinstance(blob, dict) else 0
+
+
+def run(model_name="vgg", time_steps=8, batch=64, steps=20, warmup=5, precision="bf16", lr=1e-2,
+        bucket_mb=25.0, overlap=True, seed=0, log=False, checkpoint=None):
+    """Trains for warmup+steps steps; returns a dict with samples/sec (whole job) and timings."""
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    own_group = False
+    if world > 1 and not dist.is_initialized():
+        dist.init_process_group("nccl", device_id=dev)
+        own_group = True
+
+    act_dtype = {"bf16": torch.bfloat16, "fp16": torch.float16, "fp32": torch.float32}[precision]
+    torch.backends.cudnn.benchmark = True
+    torch.manual_seed(seed)
+    net = models.build(model_name, time_steps=time_steps, act_dtype=act_dtype).to(dev)
+    model = DistributedDataParallel(net, bucket_mb=bucket_mb, overlap=overlap)
+    opt = torch.optim.SGD(net.parameters(), lr=lr, momentum=0.9)
+    data = SyntheticImages(batch, seed=1000 + rank)
+    n_params = sum(p.numel() for p in net.parameters())
+
+    def one_step(k):
+        images, labels = data.batch(k, dev)
+        model.zero_grad()
+        loss = F.cross_entropy(model(images), labels)
+        loss.backward()
+        opt.step()
+        return loss
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize(dev)
+
+    for k in range(warmup):
+        loss = one_step(k)
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0 = time.perf_counter()
+    e0.record()
+    for k in range(steps):
+        loss = one_step(warmup + k)
+        if log and rank == 0 and (k + 1) % 10 == 0:
+            print(f"step {k + 1}/{steps} loss {float(loss):.4f}", flush=True)
+    final_loss = float(loss)          # device -> host read of the step's result
+    e1.record()
+    barrier()
+    wall = time.perf_counter() - t0
+    dev_ms = e0.elapsed_time(e1)
+    if world > 1:
+        t = torch.tensor([dev_ms, wall], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        dev_ms, wall = float(t[0]), float(t[1])
+    if checkpoint and rank == 0:
+        save_checkpoint(checkpoint, model, opt, warmup + steps)
+    out = {
+        "model": model_name, "time_steps": time_steps, "batch_per_gpu": batch, "n_gpus": world,
+        "precision": precision, "params": n_params, "steps": steps,
+        "ms_per_step": dev_ms / steps, "samples_per_s": batch * world * steps / (dev_ms / 1e3),
+        "samples_per_s_wall": batch * world * steps / wall, "final_loss": final_loss,
+        "h2d_bytes_per_step": data.bytes_per_batch, "d2h_bytes_per_step": 4,
+        "grad_buckets": len(model.buckets), "overlap": overlap,
+    }
+    if own_group:
+        dist.destroy_process_group()
+    return out
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--model", default="vgg", choices=["vgg", "resnet19"])
+    ap.add_argument("--time-steps", type=int, default=None)
+    ap.add_argument("--batch", type=int, default=None)
+    ap.add_argument("--steps", type=int, default=30)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--precision", default="bf16", choices=["bf16", "fp16", "fp32"])
+    ap.add_argument("--bucket-mb", type=float, default=25.0)
+    ap.add_argument("--no-overlap", action="store_true")
+    ap.add_argument("--checkpoint", default=None)
+    ap.add_argument("--log", action="store_true")
+    a = ap.parse_args()
+    T = a.time_steps or (8 if a.model == "vgg" else 16)
+    B = a.batch or (64 if a.model == "vgg" else 128)
+    res = run(a.model, T, B, a.steps, a.warmup, a.precision, bucket_mb=a.bucket_mb,
+              overlap=not a.no_overlap, log=a.log, checkpoint=a.checkpoint)
+    if int(os.environ.get("RANK", "0")) == 0:
+        print(json.dumps(res))
+
+
+if __name__ == "__main__":
+    main()

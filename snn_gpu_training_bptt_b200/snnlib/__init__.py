@@ -54,6 +54,13 @@ def fire_bp(spatial, grad_spike, alpha, thresh, beta, interval):
 # ------------------------------------------------------------------------------------------
 # synaptic linear over time (one GEMM over the merged T*B rows)
 # ------------------------------------------------------------------------------------------
+def _cast(param, like):
+    """Parameters may be kept in fp32 while activations run in bf16/fp16: the synaptic op then
+    runs in the activation dtype (weights cast on the fly, gradients returned in the
+    parameter's dtype). With matching dtypes this is the identity."""
+    return param if param is None or param.dtype == like.dtype else param.to(like.dtype)
+
+
 def _rows(t):
     """[T, B, ...] -> [T*B, features] view (reference flattens C,H,W: snn_kernel_fp.cu:349)."""
     return t.reshape(t.shape[0] * t.shape[1], -1)
@@ -62,14 +69,15 @@ def _rows(t):
 def fc_fp(spatial, weight_fc, bias_fc):
     """fc[t] = spatial[t] @ W^T + b for every t. Reference: snn.cpp:130-136 -> snn_kernel_fp.cu:332-357."""
     T, B = spatial.shape[0], spatial.shape[1]
-    return F.linear(_rows(spatial), weight_fc, bias_fc).view(T, B, weight_fc.shape[0])
+    return F.linear(_rows(spatial), _cast(weight_fc, spatial), _cast(bias_fc, spatial)).view(
+        T, B, weight_fc.shape[0])
 
 
 def _fc_grads(inp_rows, grad_fc, weight_fc, dim_fc):
     g = _rows(grad_fc)
-    grad_in = g @ weight_fc                      # [T*B, in]
-    grad_w = g.t() @ inp_rows                    # [out, in], summed over t and b
-    grad_b = torch.sum(grad_fc, dim=tuple(dim_fc))
+    grad_in = g @ _cast(weight_fc, g)            # [T*B, in]
+    grad_w = (g.t() @ inp_rows).to(weight_fc.dtype)   # [out, in], summed over t and b
+    grad_b = torch.sum(grad_fc, dim=tuple(dim_fc), dtype=weight_fc.dtype)
     return grad_in, grad_w, grad_b
 
 
@@ -108,8 +116,8 @@ def conv_fp(spatial, weight_conv, bias_conv, stride, padding, dilation, groups, 
             deterministic):
     """conv[t] = conv2d(spatial[t]). Reference: snn.cpp:239-253 -> snn_kernel_fp.cu:457-479."""
     T, B = spatial.shape[0], spatial.shape[1]
-    y = F.conv2d(_images(spatial), weight_conv, bias_conv, tuple(stride), tuple(padding),
-                 tuple(dilation), groups)
+    y = F.conv2d(_images(spatial), _cast(weight_conv, spatial), _cast(bias_conv, spatial),
+                 tuple(stride), tuple(padding), tuple(dilation), groups)
     return y.view((T, B) + tuple(y.shape[1:]))
 
 
@@ -117,10 +125,10 @@ def _conv_grads(inp, grad_conv, weight_conv, stride, padding, dilation, groups, 
     g = _images(grad_conv)
     x = _images(inp)
     grad_in, grad_w = torch.ops.aten.convolution_backward(
-        g, x, weight_conv, None, list(stride), list(padding), list(dilation), False, [0, 0],
-        groups, [True, True, False])[:2]
-    grad_b = torch.sum(grad_conv, dim=tuple(dim_conv))
-    return grad_in, grad_w, grad_b
+        g, x, _cast(weight_conv, g), None, list(stride), list(padding), list(dilation), False,
+        [0, 0], groups, [True, True, False])[:2]
+    grad_b = torch.sum(grad_conv, dim=tuple(dim_conv), dtype=weight_conv.dtype)
+    return grad_in, grad_w.to(weight_conv.dtype), grad_b
 
 
 def conv_bp(spatial, grad_conv, weight_conv, stride, padding, dilation, groups, benchmark,

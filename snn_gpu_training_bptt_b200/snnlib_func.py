@@ -13,6 +13,7 @@ lines 25-28): membrane potentials are never stored, the backward kernel rebuilds
 import torch
 
 from . import snnlib
+from ._capi import as_time_major_dense
 
 # hyper-parameters (reference snnlib_func.py:11-17)
 alpha = 0.25
@@ -37,14 +38,14 @@ class FireFunc(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, spatial):
-        spatial = spatial.contiguous()
+        spatial = as_time_major_dense(spatial)   # no copy for contiguous or channels-last inputs
         ctx.save_for_backward(spatial)
         return snnlib.fire_s_fp(spatial, alpha, thresh)
 
     @staticmethod
     def backward(ctx, grad_spike):
         (spatial,) = ctx.saved_tensors
-        return snnlib.fire_bp(spatial, grad_spike.contiguous(), alpha, thresh, beta, interval)
+        return snnlib.fire_bp(spatial, grad_spike, alpha, thresh, beta, interval)
 
 
 fire_func = FireFunc.apply
@@ -197,7 +198,7 @@ class FireConvFunc(torch.autograd.Function):
         spatial, weight_conv, _ = ctx.saved_tensors
         stride, padding, if_bias_conv = ctx.cfg
         grads = snnlib.fire_conv_bp(
-            spatial.contiguous(), grad_conv.contiguous(), weight_conv, stride, padding, _DILATION,
+            spatial, grad_conv, weight_conv, stride, padding, _DILATION,
             _GROUPS, conv_benchmark, False, True, _DIM_CONV, alpha, thresh, beta, interval)
         return _conv_grad_tuple(grads, 0, if_bias_conv, 3)
 
@@ -219,7 +220,7 @@ class ConvFunc(torch.autograd.Function):
     def backward(ctx, grad_conv):
         spatial, weight_conv, _ = ctx.saved_tensors
         stride, padding, if_bias_conv = ctx.cfg
-        grads = snnlib.conv_bp(spatial.contiguous(), grad_conv.contiguous(), weight_conv, stride,
+        grads = snnlib.conv_bp(spatial, grad_conv, weight_conv, stride,
                                padding, _DILATION, _GROUPS, conv_benchmark, False, True, _DIM_CONV)
         return _conv_grad_tuple(grads, 0, if_bias_conv, 3)
 

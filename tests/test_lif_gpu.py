@@ -64,7 +64,7 @@ def test_reference_test_scenario_through_modules(capi, golden):
         loss.backward()
         assert np.array_equal(spikes.detach().cpu().numpy(), golden[name + "_s"])
         assert np.allclose(head.detach().cpu().numpy(), golden[name + "_head"], rtol=0, atol=1e-7)
-        assert abs(float(loss) - float(golden[name + "_loss"])) < 1e-6
+        assert abs(float(loss.detach()) - float(golden[name + "_loss"])) < 1e-6
         assert_grad_close(x.grad.cpu().numpy(), golden[name + "_gx_ce"], rtol=1e-4, atol=1e-9, what=name)
 
 
@@ -114,7 +114,8 @@ def test_sweep_T_and_ragged_N_fp32(capi, T):
         assert np.array_equal(gx.cpu().numpy(), gx_ref), (T, N)
         if b is not None:
             want = orc.c_lif_bits(x.numpy())
-            assert np.array_equal(b.cpu().numpy().reshape(-1).astype(np.int64) & 0xFFFFFFFF,
+            mask = (1 << (8 * b.element_size())) - 1      # words are stored in signed torch dtypes
+            assert np.array_equal(b.cpu().numpy().reshape(-1).astype(np.int64) & mask,
                                   want.astype(np.int64)), (T, N)
 
 

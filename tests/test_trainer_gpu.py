@@ -1,0 +1,147 @@
+"""GPU tests of the layers either side of the LIF kernels and of the example trainer:
+conv / fc wrappers against a time-stepped PyTorch composition, channels-last layouts, mixed
+precision, and the data-parallel step (NCCL ranks as child processes when >= 2 GPUs)."""
+import os
+import socket
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+import torch
+import torch.nn.functional as F
+
+from oracle import lif_oracle as orc
+from tests.helpers import CONSTS, assert_grad_close
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.fixture(scope="module", autouse=True)
+def _strict_fp32(built_lib):
+    assert torch.cuda.is_available()
+    old = (torch.backends.cuda.matmul.allow_tf32, torch.backends.cudnn.allow_tf32)
+    torch.backends.cuda.matmul.allow_tf32 = False
+    torch.backends.cudnn.allow_tf32 = False
+    yield
+    torch.backends.cuda.matmul.allow_tf32, torch.backends.cudnn.allow_tf32 = old
+
+
+def _gold_fire_conv(x, w, b, fire):
+    """Time-stepped composition as the reference's gold ops do it (gold_op.py:153-180)."""
+    s = orc.torch_fire(x, **CONSTS)[1] if fire else x
+    return torch.stack([F.conv2d(s[t], w, b, stride=1, padding=1) for t in range(x.shape[0])])
+
+
+@pytest.mark.parametrize("fire", [False, True])
+def test_conv_layers_against_time_stepped_composition(fire):
+    from snn_gpu_training_bptt_b200 import snnlib_func as sf
+    gen = torch.Generator().manual_seed(5)
+    x = (0.3 + torch.randn((6, 2, 8, 8, 8), generator=gen)).cuda()
+    w = (0.2 * torch.randn((8, 8, 3, 3), generator=gen)).cuda()
+    b = torch.randn(8, generator=gen).cuda()
+    gy = torch.randn((6, 2, 8, 8, 8), generator=gen).cuda()
+    leaves = [t.clone().requires_grad_(True) for t in (x, w, b)]
+    fn = sf.fire_conv_func if fire else sf.conv_func
+    y = fn(leaves[0], leaves[1], leaves[2], (1, 1), (1, 1), True)
+    y.backward(gy)
+    ref = [t.clone().requires_grad_(True) for t in (x, w, b)]
+    y_ref = _gold_fire_conv(ref[0], ref[1], ref[2], fire)
+    y_ref.backward(gy)
+    assert_grad_close(y.detach().cpu(), y_ref.detach().cpu(), rtol=1e-4, atol=1e-4, what="conv out")
+    for got, want, name in zip(leaves, ref, ("grad_x", "grad_w", "grad_b")):
+        assert_grad_close(got.grad.cpu(), want.grad.cpu(), rtol=1e-4, atol=2e-4, what=name)
+
+
+def test_channels_last_activations_need_no_copy_and_match():
+    """A channels-last [T*B, C, H, W] batch viewed as [T, B, C, H, W] goes through the LIF kernels
+    as it is and gives the same values as the contiguous layout."""
+    from snn_gpu_training_bptt_b200 import _capi, snnlib_func as sf
+    gen = torch.Generator().manual_seed(9)
+    x = (0.5 + torch.randn((4, 3, 16, 6, 6), generator=gen)).cuda()
+    g = torch.randn(x.shape, generator=gen).cuda()
+    x_cl = x.view(12, 16, 6, 6).contiguous(memory_format=torch.channels_last).view(4, 3, 16, 6, 6)
+    g_cl = g.view(12, 16, 6, 6).contiguous(memory_format=torch.channels_last).view(4, 3, 16, 6, 6)
+    assert not x_cl.is_contiguous() and _capi.is_time_major_dense(x_cl)
+    a = x.clone().requires_grad_(True)
+    b = x_cl.clone(memory_format=torch.preserve_format).requires_grad_(True)
+    sa, sb = sf.fire_func(a), sf.fire_func(b)
+    assert sb.stride() == x_cl.stride()
+    sa.backward(g)
+    sb.backward(g_cl)
+    assert torch.equal(sa, sb) and torch.equal(a.grad, b.grad)
+    # mismatched gradient layout is re-laid out, not misread
+    c = x_cl.clone(memory_format=torch.preserve_format).requires_grad_(True)
+    sf.fire_func(c).backward(g)
+    assert torch.equal(c.grad, a.grad)
+
+
+def test_small_vgg_fp32_against_autograd_composition():
+    """The benchmark network (narrow) end to end in fp32 vs the same network written with plain
+    PyTorch ops and the oracle's autograd LIF, both on the GPU."""
+    from snn_gpu_training_bptt_b200.example import models
+    torch.manual_seed(3)
+    net = models.SpikingVGG(time_steps=4, widths=(8, 16, 16), hidden=32, image=16,
+                            act_dtype=torch.float32).cuda()
+    images = torch.rand(3, 3, 16, 16, device="cuda")
+    labels = torch.tensor([1, 7, 3], device="cuda")
+    loss = F.cross_entropy(net(images), labels)
+    loss.backward()
+
+    def fire(x):
+        return orc.torch_fire(x, **CONSTS)[1]
+
+    def conv(x, m):
+        return torch.stack([F.conv2d(x[t], m.weight_conv, m.bias_conv, padding=1) for t in range(x.shape[0])])
+
+    def pool(x):
+        return torch.stack([F.avg_pool2d(x[t], 2) for t in range(x.shape[0])])
+
+    grads = {n: p.grad.clone() for n, p in net.named_parameters()}
+    net.zero_grad()
+    x = torch.stack([images] * 4)
+    x = pool(fire(conv(fire(conv(x, net.conv1_1)), net.conv1_2)))
+    x = pool(fire(conv(fire(conv(x, net.conv2_1)), net.conv2_2)))
+    x = pool(fire(conv(fire(conv(x, net.conv3_1)), net.conv3_2)))
+    x = x.reshape(4, 3, -1)
+    x = fire(F.linear(x, net.fc1.weight_fc, net.fc1.bias_fc))
+    loss_ref = F.cross_entropy(net.fc2(x.mean(dim=0)), labels)
+    loss_ref.backward()
+    assert abs(float(loss.detach()) - float(loss_ref.detach())) < 1e-5
+    for n, p in net.named_parameters():
+        assert_grad_close(grads[n].cpu(), p.grad.cpu(), rtol=2e-3, atol=2e-5, what=n)
+
+
+@pytest.mark.parametrize("model,T,B", [("vgg", 8, 8), ("resnet19", 4, 4)])
+def test_training_steps_run_in_bf16(model, T, B, tmp_path):
+    from snn_gpu_training_bptt_b200.example import train_synthetic
+    ck = str(tmp_path / "ck.pth.tar")
+    out = train_synthetic.run(model, time_steps=T, batch=B, steps=3, warmup=1, precision="bf16",
+                              checkpoint=ck)
+    assert np.isfinite(out["final_loss"]) and out["samples_per_s"] > 0
+    assert os.path.exists(ck)
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs >= 2 GPUs")
+def test_nccl_data_parallel_matches_single_process(tmp_path):
+    """2 NCCL ranks (child processes), each on half the batch: averaged gradients must equal the
+    single-process gradients on the whole batch. NVLS is switched off for the children."""
+    script = os.path.join(ROOT, "tests", "ddp_nccl_child.py")
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", PYTHONPATH=ROOT)
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
+           "--master-addr", "127.0.0.1", "--master-port", str(_free_port()), script, str(tmp_path)]
+    res = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+    assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-2000:]
+    r0 = torch.load(str(tmp_path / "rank0.pt"))
+    r1 = torch.load(str(tmp_path / "rank1.pt"))
+    single = torch.load(str(tmp_path / "single.pt"))
+    for name in single:
+        assert torch.equal(r0[name], r1[name]), name
+        assert_grad_close(r0[name], single[name], rtol=2e-3, atol=2e-5, what=name)
