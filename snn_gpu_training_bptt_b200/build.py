@@ -42,5 +42,20 @@ def build(force: bool = False, verbose: bool = False) -> str:
     return LIB
 
 
+def build_tuner(cache_policy=None) -> str:
+    """Build csrc/tune/lif_tune (stand-alone launch-configuration tuner; needs a GPU to run)."""
+    out = os.path.join(CSRC, "tune", "lif_tune")
+    nvcc = os.environ.get("NVCC", "nvcc")
+    cmd = [nvcc, "-O3", "-std=c++17", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo"]
+    if cache_policy is not None:
+        cmd.append(f"-DSNN_CACHE_POLICY={int(cache_policy)}")
+    subprocess.run(cmd + ["-o", out, os.path.join(CSRC, "tune", "lif_tune.cu")], check=True)
+    return out
+
+
 if __name__ == "__main__":
-    print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv))
+    if "--tuner" in sys.argv:
+        pol = sys.argv[sys.argv.index("--cache-policy") + 1] if "--cache-policy" in sys.argv else None
+        print(build_tuner(pol))
+    else:
+        print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv))
