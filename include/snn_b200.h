@@ -35,7 +35,8 @@ typedef enum snn_status {
     SNN_ERR_ALIGN = 4,       /* a pointer is not aligned to its element size */
     SNN_ERR_UNSUPPORTED = 5, /* valid request this build cannot serve (e.g. spike words with T > 32) */
     SNN_ERR_WORKSPACE = 6,   /* scratch buffer missing or too small */
-    SNN_ERR_CUDA = 7         /* the CUDA runtime reported an error at launch */
+    SNN_ERR_CUDA = 7,        /* the CUDA runtime reported an error at launch */
+    SNN_ERR_TOO_LARGE = 8    /* problem does not fit the library's built-in scratch array */
 } snn_status;
 
 /* Element type of the tensors in global memory. State is always carried in fp32
@@ -107,6 +108,39 @@ int snn_lif_bwd(const void *x, const void *grad_spike, void *grad_x, int64_t T, 
  */
 int snn_spike_unpack(const void *bits, void *spike, int64_t T, int64_t N, int dtype,
                      void *stream);
+
+/*
+ * LIF backward through time for callers that may not allocate device memory.
+ *
+ * No counterpart in the reference (its fire_bp allocates two tensors per call,
+ * snnlib/cuda/snn_kernel_bp.cu:154,160). Same arithmetic and same result as snn_lif_bwd, but
+ * this variant always takes the stored-membrane route (write u_t for all T steps, then walk
+ * them in reverse) and keeps the membrane tensor in an array that is compiled into the
+ * library instead of in caller-provided scratch. It is meant for hosts that cannot call
+ * cudaMalloc at the point where the backward runs: a serving or training process whose own
+ * allocator was handed the whole GPU up front, a latency-critical loop in which the implicit
+ * device synchronisation of cudaMalloc/cudaFree is not acceptable, or a plugin sandbox that
+ * only passes buffers in and out. Such callers still own x, grad_spike and grad_x; the
+ * library calls no cudaMalloc, cudaFree or other allocating routine here, for any T.
+ *
+ * Limits and rules
+ *   - the built-in array is SNN_STATIC_SCRATCH_BYTES (64 MiB) per GPU; every GPU on which the
+ *     library's device code is loaded holds it until the process exits;
+ *   - T * N * (4 bytes, or 8 for SNN_F64) must fit in it, otherwise SNN_ERR_TOO_LARGE is
+ *     returned and nothing is launched (e.g. fp32: T*N <= 16 Mi neuron-steps; split the neuron
+ *     axis into several calls for more);
+ *   - the first call on each device looks up the array's device address (one
+ *     cudaGetSymbolAddress, with that device current). Make that first call during set-up,
+ *     before any stream capture is begun on that device;
+ *   - all calls on one GPU share the one array. It keeps whatever the previous call left; this
+ *     entry point overwrites every element it later reads, so nothing needs clearing, but two
+ *     calls that can overlap on the GPU (different streams, no dependency) race on it. Issue
+ *     them on one stream or order them with events.
+ */
+#define SNN_STATIC_SCRATCH_BYTES (64u * 1024u * 1024u)
+int snn_lif_bwd_noalloc(const void *x, const void *grad_spike, void *grad_x, int64_t T,
+                        int64_t N, int dtype, float alpha, float thresh, float beta,
+                        float interval, void *stream);
 
 #ifdef __cplusplus
 }

@@ -27,7 +27,9 @@ SIGNATURES = {
     "snn_lif_bwd_workspace_bytes": (_i64, [_i64, _i64, _int]),
     "snn_lif_bwd": (_int, [_vp, _vp, _vp, _i64, _i64, _int, _f32, _f32, _f32, _f32, _vp, _sz, _vp]),
     "snn_spike_unpack": (_int, [_vp, _vp, _i64, _i64, _int, _vp]),
+    "snn_lif_bwd_noalloc": (_int, [_vp, _vp, _vp, _i64, _i64, _int, _f32, _f32, _f32, _f32, _vp]),
 }
+STATIC_SCRATCH_BYTES = 64 * 1024 * 1024
 
 
 class SnnError(RuntimeError):
@@ -187,3 +189,26 @@ def spike_unpack(bits, T, dtype=torch.float32):
         rc = lib().snn_spike_unpack(_ptr(bits), _ptr(out), T, N, DTYPE_CODE[dtype], _stream(bits.device))
     check("snn_spike_unpack", rc)
     return out
+
+
+def lif_bwd_noalloc(x, grad_spike, grad_x, alpha, thresh, beta, interval):
+    """snn_lif_bwd_noalloc: backward into the caller's ``grad_x`` with the membrane scratch held
+    inside the library, for callers that must not allocate on the device. All three tensors must
+    already be dense, time-major, of one dtype and layout; nothing is allocated or copied here.
+    Raises SnnError (status 8) if T*N*state bytes exceed STATIC_SCRATCH_BYTES."""
+    for name, t in (("spatial", x), ("grad_spike", grad_spike), ("grad_x", grad_x)):
+        _require_cuda(t, name)
+        if not is_time_major_dense(t):
+            raise ValueError(f"{name} must be dense and time-major (no copy is made on this path)")
+    if not (x.shape == grad_spike.shape == grad_x.shape and x.stride() == grad_spike.stride() == grad_x.stride()):
+        raise ValueError("spatial, grad_spike and grad_x must share shape and layout")
+    if not (x.dtype == grad_spike.dtype == grad_x.dtype):
+        raise TypeError("spatial, grad_spike and grad_x must share a dtype")
+    T = x.shape[0]
+    N = x.numel() // T
+    with torch.cuda.device(x.device):
+        rc = lib().snn_lif_bwd_noalloc(_ptr(x), _ptr(grad_spike), _ptr(grad_x), T, N, DTYPE_CODE[x.dtype],
+                                       float(alpha), float(thresh), float(beta), float(interval),
+                                       _stream(x.device))
+    check("snn_lif_bwd_noalloc", rc)
+    return grad_x

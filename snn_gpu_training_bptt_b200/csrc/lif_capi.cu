@@ -262,6 +262,11 @@ void unpack_pick_word(int word_bytes, int vec, const void* bits, void* spike, in
 
 }  // namespace
 
+namespace snn_internal {
+// lets other translation units of the library record the code snn_last_cuda_error() reports
+void set_last_cuda_error(int e) { g_last_cuda_error = e; }
+}  // namespace snn_internal
+
 extern "C" {
 
 int snn_version(void) { return 100; }
@@ -276,6 +281,7 @@ const char* snn_status_string(int status) {
         case SNN_ERR_UNSUPPORTED: return "request not supported";
         case SNN_ERR_WORKSPACE: return "workspace missing or too small";
         case SNN_ERR_CUDA: return "CUDA runtime error at launch";
+        case SNN_ERR_TOO_LARGE: return "problem exceeds the built-in scratch array (SNN_STATIC_SCRATCH_BYTES)";
         default: return "unknown status";
     }
 }
