@@ -109,6 +109,63 @@ int snn_lif_bwd(const void *x, const void *grad_spike, void *grad_x, int64_t T, 
 int snn_spike_unpack(const void *bits, void *spike, int64_t T, int64_t N, int dtype,
                      void *stream);
 
+/* ----------------------------------------------------------------------------------------
+ * Batch-norm family. Tensors are [T, N] time-major with N = B * C * inner; the channel of flat
+ * neuron index n is (n / inner) % C: inner = H*W for contiguous [T,B,C,H,W], inner = 1 for
+ * [T,B,C] and for channels-last images. weight / bias / var / mean / ivar / sums are fp32
+ * arrays of length C for every I/O dtype (SNN_F64 is not offered here: SNN_ERR_UNSUPPORTED).
+ * `fire` != 0 selects the BN+LIF form, 0 the plain time-major batch-norm.
+ * -------------------------------------------------------------------------------------- */
+
+/*
+ * Forward. w' = weight/sqrt(var + eps); ivar_out[c] = w'/weight[c];
+ * current = (x - mean)*w' + bias; fire: out = LIF spikes of the current (mem = u, optional);
+ * else out = current. If `var` is NULL, `ivar_out` is read as an INPUT and w' = weight*ivar:
+ * that is how the reference rebuilds spikes inside its backward functions
+ * (bn_fire_us_fp_kernel, snn_kernel_bp.cu:481-530).
+ * Replaces bn_fire_s_fp (snnlib/cuda/snn.cpp:55-66 -> snn_kernel_fp.cu:212-240, kernel
+ * :157-210) and bn_fp (snn.cpp:30-39 -> snn_kernel_fp.cu:124-150, kernel :80-122).
+ */
+int snn_bn_lif_fwd(const void *x, const float *weight, const float *bias, const float *var,
+                   const float *mean, float eps, void *out, float *mem, float *ivar_out,
+                   int64_t T, int64_t N, int64_t C, int64_t inner, int dtype, int fire,
+                   float alpha, float thresh, void *stream);
+
+/*
+ * Backward pass 1: per-channel sums over all (t, b, position) of the gradient w.r.t. the
+ * normalised current: sum_g[c] = sum gu (= grad_bias), sum_gx[c] = sum gu*xhat (= grad_weight),
+ * gu = BPTT gradient (fire) or the upstream gradient (plain BN). Both arrays are zeroed by the
+ * call (on `stream`) and accumulated with atomics. T <= 32 when fire.
+ * Replaces the sums half of bn_fire_bp / bn_fire_bp_dist1 (snn.cpp:373-387, :405-421 ->
+ * snn_kernel_bp.cu:679-750, :753-806; kernels :432-479 and :533-610) and of bn_bp / bn_bp_dist1
+ * (snn.cpp:293-303, :317-327 -> snn_kernel_bp.cu:288-345, :348-392; kernel :175-236).
+ */
+int snn_bn_lif_bwd_sums(const void *x, const void *grad, const float *weight, const float *bias,
+                        const float *ivar, const float *mean, float *sum_g, float *sum_gx,
+                        int64_t T, int64_t N, int64_t C, int64_t inner, int dtype, int fire,
+                        float alpha, float thresh, float beta, float interval, void *stream);
+
+/*
+ * gxhat[c] = weight[c]*sum_g[c]/count, gxhatx[c] = weight[c]*sum_gx[c]/count: the per-channel
+ * means the reference forms with at::mean over its per-position partial sums
+ * (snn_kernel_bp.cu:738-744). count = T*B*inner (times the world size after a sync-BN
+ * all-reduce of the sums).
+ */
+int snn_bn_channel_means(const float *sum_g, const float *sum_gx, const float *weight,
+                         float *gxhat, float *gxhatx, int64_t C, double count, void *stream);
+
+/*
+ * Backward pass 2: grad_x = gu*weight*ivar - ivar*(xhat*gxhatx[c] + gxhat[c]).
+ * Replaces the input-gradient half of bn_fire_bp / bn_fire_bp_dist2 (snn.cpp:442-460 ->
+ * snn_kernel_bp.cu:808-854; kernel :613-677) and of bn_bp / bn_bp_dist2 (snn.cpp:343-355 ->
+ * snn_kernel_bp.cu:394-425; kernel :239-285).
+ */
+int snn_bn_lif_bwd_input(const void *x, const void *grad, const float *weight, const float *bias,
+                         const float *ivar, const float *mean, const float *gxhat,
+                         const float *gxhatx, void *grad_x, int64_t T, int64_t N, int64_t C,
+                         int64_t inner, int dtype, int fire, float alpha, float thresh, float beta,
+                         float interval, void *stream);
+
 /*
  * LIF backward through time for callers that may not allocate device memory.
  *

@@ -24,6 +24,7 @@
 #include <stdint.h>
 #include <stddef.h>
 #include <math.h>
+#include <stdlib.h>
 
 #define ORACLE_MAX_T 4096
 
@@ -157,5 +158,159 @@ void oracle_lif_fwd_bits_f32(const float *x, uint32_t *bits, int64_t T, int64_t 
             w |= (uint32_t)s << t;
         }
         bits[n] = w;
+    }
+}
+
+/* =========================================================================================
+ * Batch-norm family (reference: snnlib/cuda/snn_kernel_fp.cu:80-122 bn_fp_kernel, :157-210
+ * bn_fire_s_fp_kernel; snnlib/cuda/snn_kernel_bp.cu:175-285 bn_bp_*_kernel, :432-479
+ * bn_fire_u_fp_kernel, :533-610 bn_fire_bp_wb_kernel, :613-677 bn_fire_bp_x_kernel).
+ * Layout [T, B, C, HW] contiguous. fire != 0: BN folded into the LIF input; fire == 0: plain BN.
+ * ======================================================================================= */
+
+/* forward: w' = weight/sqrt(var+eps), ivar = w'/weight, current = (x-mean)*w' + bias.
+ * If var == NULL, ivar_io is an input and w' = weight*ivar (the backward-time rebuild). */
+void oracle_bn_lif_fwd_f32(const float *x, const float *var, const float *mean, const float *weight,
+                           const float *bias, float eps, float *out, float *mem, float *ivar_io,
+                           int64_t T, int64_t B, int64_t C, int64_t HW, int fire, float alpha,
+                           float thresh)
+{
+    const int64_t CHW = C * HW, N = B * CHW;
+#pragma omp parallel for schedule(static)
+    for (int64_t i = 0; i < CHW; ++i) {
+        const int64_t c = i / HW;
+        const float m = mean[c], b = bias[c];
+        float w;
+        if (var) {
+            w = weight[c] / sqrtf(var[c] + eps);
+            if (i % HW == 0) ivar_io[c] = w / weight[c];
+        } else {
+            w = weight[c] * ivar_io[c];
+        }
+        for (int64_t bb = 0; bb < B; ++bb) {
+            float u = 0.0f;
+            int s = 0;
+            for (int64_t t = 0; t < T; ++t) {
+                const int64_t k = t * N + bb * CHW + i;
+                float cur = (x[k] - m) * w;
+                if (fire) {
+                    float leak = alpha * u;
+                    leak = leak * (float)(1 - s);
+                    u = leak + cur;
+                    u = u + b;
+                    s = u > thresh;
+                    if (out) out[k] = (float)s;
+                    if (mem) mem[k] = u;
+                } else {
+                    out[k] = cur + b;
+                }
+            }
+        }
+    }
+}
+
+/* backward. Outputs: grad_x [T,B,C,HW]; grad_weight, grad_bias, gxhat, gxhatx [C].
+ * If use_given_means != 0, gxhat/gxhatx are inputs (the second half of the sync-BN split). */
+void oracle_bn_lif_bwd_f32(const float *x, const float *grad, const float *ivar, const float *mean,
+                           const float *weight, const float *bias, float *grad_x, float *grad_weight,
+                           float *grad_bias, float *gxhat, float *gxhatx, int use_given_means,
+                           int64_t T, int64_t B, int64_t C, int64_t HW, int fire, float alpha,
+                           float thresh, float beta, float interval)
+{
+    const int64_t CHW = C * HW, N = B * CHW;
+    if (T > ORACLE_MAX_T) return;
+    /* pass 1: per-position sums in float (as the reference kernel accumulates them), combined
+     * over the positions of a channel in double */
+    double *acc = (double *)calloc((size_t)C * 4, sizeof(double));
+    for (int64_t i = 0; i < CHW; ++i) {
+        const int64_t c = i / HW;
+        const float m = mean[c], w = weight[c], iv = ivar[c], b = fire ? bias[c] : 0.0f;
+        const float wiv = w * iv;
+        float sb = 0.0f, sw = 0.0f, sx = 0.0f, sxx = 0.0f;
+        for (int64_t bb = 0; bb < B; ++bb) {
+            float ubuf[ORACLE_MAX_T];
+            if (fire) {
+                float u = 0.0f;
+                int s = 0;
+                for (int64_t t = 0; t < T; ++t) {
+                    const int64_t k = t * N + bb * CHW + i;
+                    float leak = alpha * u;
+                    leak = leak * (float)(1 - s);
+                    u = leak + (x[k] - m) * wiv;
+                    u = u + b;
+                    s = u > thresh;
+                    ubuf[t] = u;
+                }
+            }
+            float gu = 0.0f;
+            for (int64_t t = T - 1; t >= 0; --t) {
+                const int64_t k = t * N + bb * CHW + i;
+                if (fire) {
+                    const float ut = ubuf[t];
+                    const float ga = gu * alpha;
+                    float gs = 0.0f;
+                    if ((ut - thresh) < interval && (thresh - ut) < interval) gs = grad[k] - ga * ut;
+                    gu = gs * beta + ga * (float)(ut <= thresh);
+                } else {
+                    gu = grad[k];
+                }
+                const float xh = (x[k] - m) * iv;
+                sb += gu;
+                sw += gu * xh;
+                sx += gu * w;
+                sxx += gu * w * xh;
+            }
+        }
+        acc[c * 4 + 0] += sb;
+        acc[c * 4 + 1] += sw;
+        acc[c * 4 + 2] += (double)(sx / (float)(T * B));
+        acc[c * 4 + 3] += (double)(sxx / (float)(T * B));
+    }
+    for (int64_t c = 0; c < C; ++c) {
+        grad_bias[c] = (float)acc[c * 4 + 0];
+        grad_weight[c] = (float)acc[c * 4 + 1];
+        if (!use_given_means) {
+            gxhat[c] = (float)(acc[c * 4 + 2] / (double)HW);
+            gxhatx[c] = (float)(acc[c * 4 + 3] / (double)HW);
+        }
+    }
+    free(acc);
+    /* pass 2: input gradient */
+#pragma omp parallel for schedule(static)
+    for (int64_t i = 0; i < CHW; ++i) {
+        const int64_t c = i / HW;
+        const float m = mean[c], w = weight[c], iv = ivar[c], b = fire ? bias[c] : 0.0f;
+        const float wiv = w * iv, gh = gxhat[c], ghx = gxhatx[c];
+        for (int64_t bb = 0; bb < B; ++bb) {
+            float ubuf[ORACLE_MAX_T];
+            if (fire) {
+                float u = 0.0f;
+                int s = 0;
+                for (int64_t t = 0; t < T; ++t) {
+                    const int64_t k = t * N + bb * CHW + i;
+                    float leak = alpha * u;
+                    leak = leak * (float)(1 - s);
+                    u = leak + (x[k] - m) * wiv;
+                    u = u + b;
+                    s = u > thresh;
+                    ubuf[t] = u;
+                }
+            }
+            float gu = 0.0f;
+            for (int64_t t = T - 1; t >= 0; --t) {
+                const int64_t k = t * N + bb * CHW + i;
+                if (fire) {
+                    const float ut = ubuf[t];
+                    const float ga = gu * alpha;
+                    float gs = 0.0f;
+                    if ((ut - thresh) < interval && (thresh - ut) < interval) gs = grad[k] - ga * ut;
+                    gu = gs * beta + ga * (float)(ut <= thresh);
+                } else {
+                    gu = grad[k];
+                }
+                const float xh = (x[k] - m) * iv;
+                grad_x[k] = gu * w * iv - iv * (xh * ghx + gh);
+            }
+        }
     }
 }

@@ -28,6 +28,13 @@ SIGNATURES = {
     "snn_lif_bwd": (_int, [_vp, _vp, _vp, _i64, _i64, _int, _f32, _f32, _f32, _f32, _vp, _sz, _vp]),
     "snn_spike_unpack": (_int, [_vp, _vp, _i64, _i64, _int, _vp]),
     "snn_lif_bwd_noalloc": (_int, [_vp, _vp, _vp, _i64, _i64, _int, _f32, _f32, _f32, _f32, _vp]),
+    "snn_bn_lif_fwd": (_int, [_vp, _vp, _vp, _vp, _vp, _f32, _vp, _vp, _vp, _i64, _i64, _i64, _i64,
+                              _int, _int, _f32, _f32, _vp]),
+    "snn_bn_lif_bwd_sums": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64,
+                                   _int, _int, _f32, _f32, _f32, _f32, _vp]),
+    "snn_bn_channel_means": (_int, [_vp, _vp, _vp, _vp, _vp, _i64, ctypes.c_double, _vp]),
+    "snn_bn_lif_bwd_input": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64,
+                                    _i64, _int, _int, _f32, _f32, _f32, _f32, _vp]),
 }
 STATIC_SCRATCH_BYTES = 64 * 1024 * 1024
 
@@ -212,3 +219,100 @@ def lif_bwd_noalloc(x, grad_spike, grad_x, alpha, thresh, beta, interval):
                                        _stream(x.device))
     check("snn_lif_bwd_noalloc", rc)
     return grad_x
+
+
+# ----------------------------------------------------------------------------------------------
+# batch-norm family
+# ----------------------------------------------------------------------------------------------
+def _bn_geometry(x):
+    """(x made dense, T, N, C, inner) for a [T, B, C] or [T, B, C, H, W] tensor. ``inner`` is the
+    number of consecutive neurons that share a channel: H*W for the contiguous layout, 1 for
+    [T, B, C] and for channels-last images."""
+    x = as_time_major_dense(x)
+    T, C = x.shape[0], x.shape[2]
+    N = x.numel() // T
+    if x.dim() == 3 or x.numel() == 0:
+        return x, T, N, C, 1
+    if x.is_contiguous():
+        return x, T, N, C, N // (x.shape[1] * C)
+    if x.stride(2) == 1:                       # channels-last: channel is the fastest axis
+        return x, T, N, C, 1
+    x = x.contiguous()
+    return x, T, N, C, N // (x.shape[1] * C)
+
+
+def _f32c(t, C, name):
+    if t.dtype != torch.float32 or not t.is_cuda or t.numel() != C:
+        raise TypeError(f"{name} must be a float32 CUDA tensor with {C} elements")
+    return t.contiguous()
+
+
+def bn_lif_fwd(x, weight, bias, var, mean, eps, alpha, thresh, fire=True, want_mem=False, ivar=None):
+    """snn_bn_lif_fwd. Returns (ivar, out, mem): out = spikes (fire) or the normalised tensor.
+    Pass ``var=None, ivar=<tensor>`` to rebuild with w' = weight*ivar (backward-time form)."""
+    _require_cuda(x, "spatial")
+    if x.dtype == torch.float64:
+        raise TypeError("the batch-norm family supports float32, bfloat16 and float16")
+    x, T, N, C, inner = _bn_geometry(x)
+    w, b, m = (_f32c(t, C, n) for t, n in ((weight, "weight_bn"), (bias, "bias_bn"), (mean, "mean")))
+    v = _f32c(var, C, "var") if var is not None else None
+    with torch.cuda.device(x.device):
+        out = torch.empty_like(x)
+        mem = torch.empty_like(x, dtype=torch.float32) if (want_mem and fire) else None
+        ivar = torch.empty_like(w) if v is not None else _f32c(ivar, C, "ivar")
+        if N == 0:
+            return ivar, out, mem
+        rc = lib().snn_bn_lif_fwd(_ptr(x), _ptr(w), _ptr(b), _ptr(v), _ptr(m), float(eps), _ptr(out),
+                                  _ptr(mem), _ptr(ivar), T, N, C, inner, DTYPE_CODE[x.dtype], int(fire),
+                                  float(alpha), float(thresh), _stream(x.device))
+    check("snn_bn_lif_fwd", rc)
+    return ivar, out, mem
+
+
+def bn_lif_bwd_sums(x, grad, weight, bias, ivar, mean, alpha, thresh, beta, interval, fire=True):
+    """snn_bn_lif_bwd_sums. Returns (x_dense, grad_dense, sum_g, sum_gx, count) where count is the
+    number of values per channel (T*B*inner)."""
+    _require_cuda(x, "spatial")
+    _require_cuda(grad, "grad")
+    x, T, N, C, inner = _bn_geometry(x)
+    g = like_layout(grad, x)
+    w, b, iv, m = (_f32c(t, C, n) for t, n in ((weight, "weight_bn"), (bias, "bias_bn"), (ivar, "ivar"), (mean, "mean")))
+    with torch.cuda.device(x.device):
+        sums = torch.empty((2, C), dtype=torch.float32, device=x.device)
+        rc = lib().snn_bn_lif_bwd_sums(_ptr(x), _ptr(g), _ptr(w), _ptr(b), _ptr(iv), _ptr(m), _ptr(sums[0]),
+                                       _ptr(sums[1]), T, N, C, inner, DTYPE_CODE[x.dtype], int(fire),
+                                       float(alpha), float(thresh), float(beta), float(interval),
+                                       _stream(x.device))
+    check("snn_bn_lif_bwd_sums", rc)
+    return x, g, sums[0], sums[1], T * N // C
+
+
+def bn_channel_means(sum_g, sum_gx, weight, count):
+    C = sum_g.numel()
+    with torch.cuda.device(sum_g.device):
+        out = torch.empty((2, C), dtype=torch.float32, device=sum_g.device)
+        rc = lib().snn_bn_channel_means(_ptr(sum_g), _ptr(sum_gx), _ptr(_f32c(weight, C, "weight_bn")),
+                                        _ptr(out[0]), _ptr(out[1]), C, float(count), _stream(sum_g.device))
+    check("snn_bn_channel_means", rc)
+    return out[0], out[1]
+
+
+def bn_lif_bwd_input(x, grad, weight, bias, ivar, mean, gxhat, gxhatx, alpha, thresh, beta, interval,
+                     fire=True):
+    """snn_bn_lif_bwd_input. Returns grad_x laid out like x."""
+    _require_cuda(x, "spatial")
+    x, T, N, C, inner = _bn_geometry(x)
+    g = like_layout(grad, x)
+    w, b, iv, m, gh, ghx = (_f32c(t, C, n) for t, n in (
+        (weight, "weight_bn"), (bias, "bias_bn"), (ivar, "ivar"), (mean, "mean"),
+        (gxhat.reshape(-1), "grad_xhat"), (gxhatx.reshape(-1), "grad_xhatx")))
+    with torch.cuda.device(x.device):
+        gx = torch.empty_like(x)
+        if N == 0:
+            return gx
+        rc = lib().snn_bn_lif_bwd_input(_ptr(x), _ptr(g), _ptr(w), _ptr(b), _ptr(iv), _ptr(m), _ptr(gh),
+                                        _ptr(ghx), _ptr(gx), T, N, C, inner, DTYPE_CODE[x.dtype], int(fire),
+                                        float(alpha), float(thresh), float(beta), float(interval),
+                                        _stream(x.device))
+    check("snn_bn_lif_bwd_input", rc)
+    return gx

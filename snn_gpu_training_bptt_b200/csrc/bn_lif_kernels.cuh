@@ -1,0 +1,333 @@
+// Batch-norm affine (per channel) in front of the LIF recurrence, and plain time-major
+// batch-norm: device code for sm_100a.
+//
+// Reference behaviour (liangling76/snn_gpu_training_bptt):
+//   forward   snnlib/cuda/snn_kernel_fp.cu:157-210 (bn_fire_s_fp_kernel), :80-122 (bn_fp_kernel)
+//               w' = weight[c] / sqrt(var[c] + eps) ;  ivar[c] = w' / weight[c]
+//               current_t = (x_t - mean[c]) * w' + bias[c] ;  LIF on current_t  (or y = current)
+//   backward  snnlib/cuda/snn_kernel_bp.cu:432-479 (u rebuilt with w' = weight[c]*ivar[c]),
+//             :533-610 (per-channel sums), :613-677 (input gradient); plain BN :175-285
+//               gu_t  = BPTT gradient w.r.t. current_t      (= upstream gradient for plain BN)
+//               xhat  = (x_t - mean[c]) * ivar[c]
+//               grad_bias[c] = sum gu ;  grad_weight[c] = sum gu*xhat
+//               gxhat[c] = mean(gu*weight[c]) ;  gxhatx[c] = mean(gu*weight[c]*xhat)
+//               grad_x_t = gu*weight[c]*ivar[c] - ivar[c]*(xhat*gxhatx[c] + gxhat[c])
+//
+// The reference runs backward as three full passes (rebuild u into a tensor, a sums pass that
+// runs BPTT, an input-gradient pass that runs BPTT again: 36 B per neuron-step in fp32). Here
+// it is two passes that each rebuild u and gu in registers: the sums pass reads x and g (8 B),
+// the input-gradient pass reads x and g and writes grad_x (12 B). Between the two passes sits
+// the only cross-thread dependency, the per-channel means; that is also exactly where the
+// sync-BN variants all-reduce them across GPUs.
+//
+// Layout: [T, N] time-major; the channel of neuron n (flat index inside one time step) is
+// (n / inner) % C: inner = H*W for contiguous [T,B,C,H,W], inner = 1 for [T,B,C] and for
+// channels-last images. BN parameters and statistics are fp32 arrays of length C whatever the
+// I/O type; sums are accumulated hierarchically (registers over T and the thread's neurons,
+// warp shuffles when a warp sits inside one channel, shared-memory atomics per CTA, then one
+// global atomicAdd per (CTA, channel)).
+#pragma once
+#include "lif_kernels.cuh"
+
+namespace snn {
+
+struct BnParams {
+    const float* mean;     // [C]
+    const float* weight;   // [C]
+    const float* bias;     // [C]  (forward / u rebuild only)
+    const float* var;      // [C]  forward only
+    const float* ivar;     // [C]  backward only
+    float eps;
+    long long inner;       // neurons per channel run
+    int C;
+};
+
+__device__ __forceinline__ int channel_of(long long n, long long inner, int C) {
+    return static_cast<int>((n / inner) % C);
+}
+
+// current = ((leak + (x - m) * w) + b), operations rounded one by one, association as in
+// the reference expression `alpha*u*(1-s) + (x - m)*w + b` read left to right.
+__device__ __forceinline__ float bn_lif_step(float u, float gate, float x, float m, float w, float b,
+                                             float alpha) {
+    const float leak = mul_rn(mul_rn(alpha, u), gate);
+    return add_rn(add_rn(leak, mul_rn(sub_rn(x, m), w)), b);
+}
+
+// ---------------------------------------------------------------------------------------
+// Forward: FIRE=true -> spikes (and optionally u); FIRE=false -> y = (x-m)*w' + b.
+// With p.var given it also writes ivar[c] (by the thread that owns the first neuron of channel
+// c in batch 0); with p.var == nullptr it reads p.ivar instead and uses w' = weight*ivar, which
+// is how the reference rebuilds spikes inside its backward functions.
+// ---------------------------------------------------------------------------------------
+template <typename IO, int VEC, int TC, bool FIRE>
+__global__ void bn_lif_fwd_kernel(const IO* __restrict__ x, IO* __restrict__ out,
+                                  float* __restrict__ mem, float* __restrict__ ivar_out,
+                                  BnParams p, int T, long long N, float alpha, float thresh)
+{
+    const long long i = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) * VEC;
+    if (i >= N) return;
+    float m[VEC], w[VEC], b[VEC];
+#pragma unroll
+    for (int v = 0; v < VEC; ++v) {
+        const int c = channel_of(i + v, p.inner, p.C);
+        const float wt = p.weight[c];
+        m[v] = p.mean[c];
+        b[v] = p.bias[c];
+        if (p.var != nullptr) {
+            w[v] = wt / sqrtf(p.var[c] + p.eps);      // IEEE division and square root
+            if (ivar_out != nullptr && (i + v) < p.inner * p.C && (i + v) % p.inner == 0)
+                ivar_out[c] = w[v] / wt;
+        } else {
+            w[v] = mul_rn(wt, p.ivar[c]);             // backward-time rebuild: w' = weight*ivar
+        }
+    }
+    float u[VEC], gate[VEC];
+#pragma unroll
+    for (int v = 0; v < VEC; ++v) { u[v] = 0.f; gate[v] = 1.f; }
+
+    for (int t0 = 0; t0 < T; t0 += TC) {
+        Pack<IO, VEC> xin[TC];
+#pragma unroll
+        for (int k = 0; k < TC; ++k)
+            if (t0 + k < T) xin[k] = ld_stream<IO, VEC>(x + static_cast<long long>(t0 + k) * N + i);
+#pragma unroll
+        for (int k = 0; k < TC; ++k) {
+            if (t0 + k < T) {
+                Pack<IO, VEC> o;
+                Pack<float, VEC> mm;
+#pragma unroll
+                for (int v = 0; v < VEC; ++v) {
+                    const float xv = Elem<IO>::load(xin[k].v[v]);
+                    if (FIRE) {
+                        u[v] = bn_lif_step(u[v], gate[v], xv, m[v], w[v], b[v], alpha);
+                        const bool s = u[v] > thresh;
+                        gate[v] = s ? 0.f : 1.f;
+                        o.v[v] = Elem<IO>::store(s ? 1.f : 0.f);
+                        mm.v[v] = u[v];
+                    } else {
+                        o.v[v] = Elem<IO>::store(add_rn(mul_rn(sub_rn(xv, m[v]), w[v]), b[v]));
+                    }
+                }
+                const long long off = static_cast<long long>(t0 + k) * N + i;
+                if (out != nullptr) st_stream<IO, VEC>(out + off, o);
+                if (FIRE && mem != nullptr) st_stream<float, VEC>(mem + off, mm);
+            }
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------
+// Shared by both backward passes: rebuild u (w' = weight*ivar, as the reference's backward
+// does) and run the reverse-time recurrence, leaving gu[t][v] in registers.
+// ---------------------------------------------------------------------------------------
+template <typename IO, int VEC, int TMAX, bool FIRE>
+__device__ __forceinline__ void bn_lif_grad_current(const Pack<IO, VEC> (&xin)[TMAX],
+                                                    const Pack<IO, VEC> (&gin)[TMAX], int T,
+                                                    const float (&m)[VEC], const float (&wiv)[VEC],
+                                                    const float (&b)[VEC], float alpha, float thresh,
+                                                    float beta, float interval,
+                                                    float (&gu_out)[TMAX][VEC])
+{
+    if constexpr (!FIRE) {
+#pragma unroll
+        for (int t = 0; t < TMAX; ++t)
+            if (t < T) {
+#pragma unroll
+                for (int v = 0; v < VEC; ++v) gu_out[t][v] = Elem<IO>::load(gin[t].v[v]);
+            }
+    } else {
+    float u[TMAX][VEC];
+    float uu[VEC], gate[VEC];
+#pragma unroll
+    for (int v = 0; v < VEC; ++v) { uu[v] = 0.f; gate[v] = 1.f; }
+#pragma unroll
+    for (int t = 0; t < TMAX; ++t) {
+        if (t < T) {
+#pragma unroll
+            for (int v = 0; v < VEC; ++v) {
+                uu[v] = bn_lif_step(uu[v], gate[v], Elem<IO>::load(xin[t].v[v]), m[v], wiv[v], b[v], alpha);
+                gate[v] = (uu[v] > thresh) ? 0.f : 1.f;
+                u[t][v] = uu[v];
+            }
+        }
+    }
+    float gu[VEC];
+#pragma unroll
+    for (int v = 0; v < VEC; ++v) gu[v] = 0.f;
+#pragma unroll
+    for (int t = TMAX - 1; t >= 0; --t) {
+        if (t < T) {
+#pragma unroll
+            for (int v = 0; v < VEC; ++v) {
+                const float ut = u[t][v];
+                const float ga = mul_rn(gu[v], alpha);
+                const bool inside = (sub_rn(ut, thresh) < interval) && (sub_rn(thresh, ut) < interval);
+                float gs = 0.f;
+                if (inside) gs = sub_rn(Elem<IO>::load(gin[t].v[v]), mul_rn(ga, ut));
+                const float keep = (ut <= thresh) ? 1.f : 0.f;
+                gu[v] = add_rn(mul_rn(gs, beta), mul_rn(ga, keep));
+                gu_out[t][v] = gu[v];
+            }
+        }
+    }
+    }  // FIRE
+}
+
+// ---------------------------------------------------------------------------------------
+// Backward pass 1: per-channel sums  sum_g[c] += gu ,  sum_gx[c] += gu * xhat.
+// sums must be zero before the launch. Dynamic shared memory: 2 * nq floats, nq = number of
+// distinct channel runs a CTA can touch (host computes (span + inner - 1)/inner + 1).
+// ---------------------------------------------------------------------------------------
+template <typename IO, int VEC, int TMAX, bool FIRE>
+__global__ void bn_lif_bwd_sums_kernel(const IO* __restrict__ x, const IO* __restrict__ g,
+                                       float* __restrict__ sum_g, float* __restrict__ sum_gx,
+                                       BnParams p, int T, long long N, int nq, float alpha,
+                                       float thresh, float beta, float interval)
+{
+    extern __shared__ float sacc[];                       // [2][nq]
+    for (int j = threadIdx.x; j < 2 * nq; j += blockDim.x) sacc[j] = 0.f;
+    __syncthreads();
+
+    const long long blk0 = static_cast<long long>(blockIdx.x) * blockDim.x * VEC;
+    const long long q0 = blk0 / p.inner;
+    const long long i = blk0 + static_cast<long long>(threadIdx.x) * VEC;
+    const bool active = i < N;
+
+    float s1[VEC], s2[VEC];
+    long long q[VEC];
+#pragma unroll
+    for (int v = 0; v < VEC; ++v) { s1[v] = 0.f; s2[v] = 0.f; q[v] = q0; }
+
+    if (active) {
+        float m[VEC], wiv[VEC], b[VEC], iv[VEC];
+#pragma unroll
+        for (int v = 0; v < VEC; ++v) {
+            q[v] = (i + v) / p.inner;
+            const int c = static_cast<int>(q[v] % p.C);
+            m[v] = p.mean[c];
+            iv[v] = p.ivar[c];
+            wiv[v] = mul_rn(p.weight[c], iv[v]);
+            b[v] = FIRE ? p.bias[c] : 0.f;
+        }
+        Pack<IO, VEC> xin[TMAX], gin[TMAX];
+#pragma unroll
+        for (int t = 0; t < TMAX; ++t)
+            if (t < T) xin[t] = ld_stream<IO, VEC>(x + static_cast<long long>(t) * N + i);
+#pragma unroll
+        for (int t = 0; t < TMAX; ++t)
+            if (t < T) gin[t] = ld_stream<IO, VEC>(g + static_cast<long long>(t) * N + i);
+        float gu[TMAX][VEC];
+        bn_lif_grad_current<IO, VEC, TMAX, FIRE>(xin, gin, T, m, wiv, b, alpha, thresh, beta, interval, gu);
+#pragma unroll
+        for (int t = 0; t < TMAX; ++t) {
+            if (t < T) {
+#pragma unroll
+                for (int v = 0; v < VEC; ++v) {
+                    const float xhat = mul_rn(sub_rn(Elem<IO>::load(xin[t].v[v]), m[v]), iv[v]);
+                    s1[v] += gu[t][v];
+                    s2[v] = fmaf(gu[t][v], xhat, s2[v]);
+                }
+            }
+        }
+    }
+
+    // warp inside one channel run: butterfly, one shared atomic per warp; otherwise per lane
+    const long long q_first = __shfl_sync(0xffffffffu, q[0], 0);
+    const bool same = __all_sync(0xffffffffu, (!active) || (q[0] == q_first && q[VEC - 1] == q_first));
+    if (same) {
+        float a = 0.f, c2 = 0.f;
+#pragma unroll
+        for (int v = 0; v < VEC; ++v) { a += s1[v]; c2 += s2[v]; }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            a += __shfl_xor_sync(0xffffffffu, a, o);
+            c2 += __shfl_xor_sync(0xffffffffu, c2, o);
+        }
+        if ((threadIdx.x & 31) == 0) {
+            const int j = static_cast<int>(q_first - q0);
+            atomicAdd(&sacc[j], a);
+            atomicAdd(&sacc[nq + j], c2);
+        }
+    } else if (active) {
+#pragma unroll
+        for (int v = 0; v < VEC; ++v) {
+            const int j = static_cast<int>(q[v] - q0);
+            atomicAdd(&sacc[j], s1[v]);
+            atomicAdd(&sacc[nq + j], s2[v]);
+        }
+    }
+    __syncthreads();
+    for (int j = threadIdx.x; j < nq; j += blockDim.x) {
+        const float a = sacc[j], c2 = sacc[nq + j];
+        if (a != 0.f || c2 != 0.f) {
+            const int c = static_cast<int>((q0 + j) % p.C);
+            atomicAdd(&sum_g[c], a);
+            atomicAdd(&sum_gx[c], c2);
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------
+// Backward pass 2: grad_x = gu*w*ivar - ivar*(xhat*gxhatx[c] + gxhat[c]).
+// ---------------------------------------------------------------------------------------
+template <typename IO, int VEC, int TMAX, bool FIRE>
+__global__ void bn_lif_bwd_input_kernel(const IO* __restrict__ x, const IO* __restrict__ g,
+                                        const float* __restrict__ gxhat,
+                                        const float* __restrict__ gxhatx, IO* __restrict__ gx,
+                                        BnParams p, int T, long long N, float alpha, float thresh,
+                                        float beta, float interval)
+{
+    const long long i = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) * VEC;
+    if (i >= N) return;
+    float m[VEC], wiv[VEC], b[VEC], iv[VEC], wt[VEC], gh[VEC], ghx[VEC];
+#pragma unroll
+    for (int v = 0; v < VEC; ++v) {
+        const int c = channel_of(i + v, p.inner, p.C);
+        m[v] = p.mean[c];
+        iv[v] = p.ivar[c];
+        wt[v] = p.weight[c];
+        wiv[v] = mul_rn(wt[v], iv[v]);
+        b[v] = FIRE ? p.bias[c] : 0.f;
+        gh[v] = gxhat[c];
+        ghx[v] = gxhatx[c];
+    }
+    Pack<IO, VEC> xin[TMAX], gin[TMAX];
+#pragma unroll
+    for (int t = 0; t < TMAX; ++t)
+        if (t < T) xin[t] = ld_stream<IO, VEC>(x + static_cast<long long>(t) * N + i);
+#pragma unroll
+    for (int t = 0; t < TMAX; ++t)
+        if (t < T) gin[t] = ld_stream<IO, VEC>(g + static_cast<long long>(t) * N + i);
+    float gu[TMAX][VEC];
+    bn_lif_grad_current<IO, VEC, TMAX, FIRE>(xin, gin, T, m, wiv, b, alpha, thresh, beta, interval, gu);
+#pragma unroll
+    for (int t = 0; t < TMAX; ++t) {
+        if (t < T) {
+            Pack<IO, VEC> o;
+#pragma unroll
+            for (int v = 0; v < VEC; ++v) {
+                const float xhat = mul_rn(sub_rn(Elem<IO>::load(xin[t].v[v]), m[v]), iv[v]);
+                const float lhs = mul_rn(mul_rn(gu[t][v], wt[v]), iv[v]);
+                const float rhs = mul_rn(iv[v], add_rn(mul_rn(xhat, ghx[v]), gh[v]));
+                o.v[v] = Elem<IO>::store(sub_rn(lhs, rhs));
+            }
+            st_stream<IO, VEC>(gx + static_cast<long long>(t) * N + i, o);
+        }
+    }
+}
+
+// gxhat[c] = weight[c]*sum_g[c]/count ; gxhatx[c] = weight[c]*sum_gx[c]/count  (C threads)
+__global__ void bn_channel_means_kernel(const float* __restrict__ sum_g,
+                                        const float* __restrict__ sum_gx,
+                                        const float* __restrict__ weight, float* __restrict__ gxhat,
+                                        float* __restrict__ gxhatx, int C, float inv_count)
+{
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c < C) {
+        gxhat[c] = weight[c] * sum_g[c] * inv_count;
+        gxhatx[c] = weight[c] * sum_gx[c] * inv_count;
+    }
+}
+
+}  // namespace snn

@@ -114,9 +114,124 @@ class SpikingResNet19(nn.Module):
         return self.fc2(x.mean(dim=0).float())
 
 
+# ------------------------------------------------------------------------------------------
+# The reference's own (batch-norm based) networks, with its attribute names so that state
+# dicts saved by the reference's scripts load here and vice versa (reference models.py:8-191).
+# T is read from snnlib_func.time_step at call time, as the reference does.
+# ------------------------------------------------------------------------------------------
+class _BnNet(nn.Module):
+    """Shared: direct encoding over snnlib_func.time_step steps and the train_bn switch."""
+
+    def _encode(self, images):
+        return images.unsqueeze(0).expand((sf.time_step,) + tuple(images.shape)).contiguous()
+
+    def _bn_layers(self):
+        return [m for m in self.modules() if hasattr(m, "train_bn")]
+
+    def set_bn(self, train_bn):
+        """True: normalise with batch statistics and update the running ones; False: use the
+        running statistics (reference models.py:37-39)."""
+        for layer in self._bn_layers():
+            layer.train_bn = train_bn
+
+
+class CIFAR_BN(_BnNet):
+    """9 conv (stride-2 convs instead of pooling) + 2 fc + BN-LIF + linear, 32x32 inputs.
+    Reference: models.py:8-60."""
+
+    def __init__(self):
+        super().__init__()
+        self.conv1_1 = sop.Conv(3, 128)
+        plan = [("conv1_2", 128, 128, 1), ("conv1_3", 128, 128, 2), ("conv2_1", 128, 256, 1),
+                ("conv2_2", 256, 256, 1), ("conv2_3", 256, 256, 2), ("conv3_1", 256, 512, 1),
+                ("conv3_2", 512, 512, 1), ("conv3_3", 512, 512, 2)]
+        for name, cin, cout, stride in plan:
+            setattr(self, name, sop.BnFireConv(cin, cout, stride=(stride, stride)))
+        self._conv_order = ["conv1_1"] + [p[0] for p in plan]
+        self.fc1 = sop.BnFireFc(4 * 4 * 512, 1024, dim_bn=(0, 1, 3, 4), cin_bn=512)
+        self.fc2 = sop.BnFireFc(1024, 512, dim_bn=(0, 1))
+        self.bn = sop.BnFire(512, dim_bn=(0, 1))
+        self.fc3 = nn.Linear(512, 10)
+
+    def forward(self, images):
+        x = self._encode(images)
+        for name in self._conv_order:
+            x = getattr(self, name)(x)
+        x = self.bn(self.fc2(self.fc1(x)))
+        return self.fc3(x.mean(dim=0))
+
+
+class Alexnet_BN_DIST(_BnNet):
+    """AlexNet-style, sync-BN layers, 224x224 inputs, 1000 classes. Reference: models.py:62-103."""
+
+    def __init__(self):
+        super().__init__()
+        self.conv1 = sop.Conv(3, 64, stride=(2, 2))
+        plan = [(64, 128, 2), (128, 256, 2), (256, 256, 2), (256, 384, 1), (384, 256, 1), (256, 256, 2)]
+        for k, (cin, cout, stride) in enumerate(plan, start=2):
+            setattr(self, f"conv{k}", sop.BnFireConvDist(cin, cout, stride=(stride, stride)))
+        self.fc1 = sop.BnFireFcDist(7 * 7 * 256, 4096, dim_bn=(0, 1, 3, 4), cin_bn=256)
+        self.fc2 = sop.BnFireFcDist(4096, 4096, dim_bn=(0, 1))
+        self.fire = sop.Fire()
+        self.fc3 = nn.Linear(4096, 1000)
+
+    def forward(self, images):
+        x = self._encode(images)
+        for k in range(1, 8):
+            x = getattr(self, f"conv{k}")(x)
+        x = self.fire(self.fc2(self.fc1(x)))
+        return self.fc3(x.mean(dim=0))
+
+
+class ResidualDist(nn.Module):
+    """LIF-conv, BN-LIF-conv, BN, plus the (optionally projected) input. Reference: models.py:107-128."""
+
+    def __init__(self, cin, cout, stride=(1, 1), downsample=None):
+        super().__init__()
+        self.conv1 = sop.FireConv(cin, cout, stride=stride)
+        self.conv2 = sop.BnFireConvDist(cout, cout)
+        self.bn2 = sop.BnDist(cout, dim_bn=(0, 1, 3, 4))
+        self.downsample = downsample
+
+    def forward(self, current):
+        out = self.bn2(self.conv2(self.conv1(current)))
+        return out + (self.downsample(current) if self.downsample is not None else current)
+
+
+class Resnet_DIST(_BnNet):
+    """ResNet-34 layout (3-4-6-3 blocks), sync-BN, 224x224 inputs. Reference: models.py:132-191."""
+
+    def __init__(self):
+        super().__init__()
+        self.pre_conv = sop.Conv(3, 64, kernel_size=(7, 7), stride=(2, 2), padding=(3, 3))
+        self.pre_bn = sop.BnDist(64, dim_bn=(0, 1, 3, 4))
+        cin = 64
+        for k, (cout, blocks) in enumerate(((64, 3), (128, 4), (256, 6), (512, 3)), start=1):
+            setattr(self, f"layer{k}", self._stage(cin, cout, blocks))
+            cin = cout
+        self.fire = sop.Fire()
+        self.fc = nn.Linear(512, 1000)
+
+    @staticmethod
+    def _stage(cin, cout, blocks, stride=(2, 2)):
+        project = nn.Sequential(sop.FireConv(cin, cout, kernel_size=(1, 1), stride=stride, padding=(0, 0)),
+                                sop.BnDist(cout, (0, 1, 3, 4)))
+        return nn.Sequential(ResidualDist(cin, cout, stride, project),
+                             *[ResidualDist(cout, cout) for _ in range(1, blocks)])
+
+    def forward(self, images):
+        x = self.pre_bn(self.pre_conv(self._encode(images)))
+        for k in range(1, 5):
+            x = getattr(self, f"layer{k}")(x)
+        x = self.fire(x).mean(dim=0)
+        return self.fc(F.avg_pool2d(x, 7).flatten(1))
+
+
 def build(name, **kw):
     if name == "vgg":
         return SpikingVGG(**kw)
     if name == "resnet19":
         return SpikingResNet19(**kw)
+    if name in ("cifar_bn", "alexnet_bn_dist", "resnet_dist"):
+        return {"cifar_bn": CIFAR_BN, "alexnet_bn_dist": Alexnet_BN_DIST, "resnet_dist": Resnet_DIST}[name]()
     raise ValueError(f"unknown model {name!r}")

@@ -105,7 +105,7 @@ def run(model_name="vgg", time_steps=8, batch=64, steps=20, warmup=5, precision=
         loss = one_step(warmup + k)
         if log and rank == 0 and (k + 1) % 10 == 0:
             print(f"step {k + 1}/{steps} loss {float(loss):.4f}", flush=True)
-    final_loss = float(loss)          # device -> host read of the step's result
+    final_loss = float(loss.detach())  # device -> host read of the step's result
     e1.record()
     barrier()
     wall = time.perf_counter() - t0

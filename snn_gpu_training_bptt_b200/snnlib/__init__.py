@@ -3,9 +3,9 @@
 The reference builds ``snnlib`` from snnlib/cuda/snn.cpp (pybind11 table at snn.cpp:798-830)
 and its only caller is snnlib/example/snnlib_func.py. This package exposes the same function
 names with the same positional arguments and return values, backed by libsnn_b200.so
-(hand-written sm_100a kernels behind a C ABI, see include/snn_b200.h) for the LIF fire path
-and by one library GEMM / convolution over the merged [T*B, ...] batch where the reference
-issues T separate cuBLAS / cuDNN calls.
+(hand-written sm_100a kernels behind a C ABI, see include/snn_b200.h) for the LIF fire path and
+the batch-norm family, and by one library GEMM / convolution over the merged [T*B, ...] batch
+where the reference issues T separate cuBLAS / cuDNN calls.
 
 Make it importable under the reference's name with either
 ``snn_gpu_training_bptt_b200.install_as_snnlib()`` or by putting this package's parent
@@ -158,28 +158,137 @@ def fire_conv_bp(spatial, grad_conv, weight_conv, stride, padding, dilation, gro
 
 
 # ------------------------------------------------------------------------------------------
-# batch-norm family: names of the reference's table that are not built yet
+# batch-norm family. Statistics (var, mean) come from the caller, as in the reference, where
+# snnlib_op computes them with torch.var_mean / all-reduced means before calling in.
 # ------------------------------------------------------------------------------------------
-def _not_built(name, where):
-    def stub(*args, **kwargs):
-        raise NotImplementedError(
-            f"snnlib.{name} (reference: snnlib/cuda/snn.cpp:{where}) is outside the LIF fire "
-            "path this library implements; no substitute implementation is provided")
-    stub.__name__ = name
-    return stub
+def bn_fp(x_bn, weight_bn, bias_bn, var, mean, eps_bn):
+    """Returns [ivar, y_bn]. Reference: snn.cpp:30-39 -> snn_kernel_fp.cu:124-150."""
+    ivar, y, _ = _capi.bn_lif_fwd(x_bn, weight_bn, bias_bn, var, mean, eps_bn, 0.0, 0.0, fire=False)
+    return [ivar, y]
 
 
-bn_fp = _not_built("bn_fp", "30-39")
-bn_bp = _not_built("bn_bp", "293-303")
-bn_fire_s_fp = _not_built("bn_fire_s_fp", "55-66")
-bn_fire_bp = _not_built("bn_fire_bp", "373-387")
-bn_fire_fc_fp = _not_built("bn_fire_fc_fp", "85-101")
-bn_fire_fc_bp = _not_built("bn_fire_fc_bp", "484-504")
-bn_fire_conv_fp = _not_built("bn_fire_conv_fp", "162-187")
-bn_fire_conv_bp = _not_built("bn_fire_conv_bp", "630-658")
-bn_bp_dist1 = _not_built("bn_bp_dist1", "317-327")
-bn_bp_dist2 = _not_built("bn_bp_dist2", "343-355")
-bn_fire_bp_dist1 = _not_built("bn_fire_bp_dist1", "405-421")
-bn_fire_bp_dist2 = _not_built("bn_fire_bp_dist2", "442-460")
-bn_fire_fc_bp_dist1 = _not_built("bn_fire_fc_bp_dist1", "528-551")
-bn_fire_conv_bp_dist1 = _not_built("bn_fire_conv_bp_dist1", "687-716")
+def bn_fire_s_fp(spatial, weight_bn, bias_bn, var, mean, eps_bn, alpha, thresh):
+    """Returns [ivar, spike]. Reference: snn.cpp:55-66 -> snn_kernel_fp.cu:212-240."""
+    ivar, spike, _ = _capi.bn_lif_fwd(spatial, weight_bn, bias_bn, var, mean, eps_bn, alpha, thresh)
+    return [ivar, spike]
+
+
+def _bn_backward(x, grad, weight_bn, bias_bn, ivar, mean, consts, fire):
+    """Two-pass backward: per-channel sums, channel means, input gradient."""
+    alpha, thresh, beta, interval = consts
+    x, g, sum_g, sum_gx, count = _capi.bn_lif_bwd_sums(x, grad, weight_bn, bias_bn, ivar, mean, alpha,
+                                                       thresh, beta, interval, fire=fire)
+    gxhat, gxhatx = _capi.bn_channel_means(sum_g, sum_gx, weight_bn, count)
+    gx = _capi.bn_lif_bwd_input(x, g, weight_bn, bias_bn, ivar, mean, gxhat, gxhatx, alpha, thresh,
+                                beta, interval, fire=fire)
+    return gx, sum_gx, sum_g          # grad_x, grad_weight_bn, grad_bias_bn
+
+
+def _bn_backward_local(x, grad, weight_bn, bias_bn, ivar, mean, consts, fire):
+    """First half for sync-BN: local channel means (to be all-reduced) and local parameter sums."""
+    alpha, thresh, beta, interval = consts
+    _, _, sum_g, sum_gx, count = _capi.bn_lif_bwd_sums(x, grad, weight_bn, bias_bn, ivar, mean, alpha,
+                                                       thresh, beta, interval, fire=fire)
+    gxhat, gxhatx = _capi.bn_channel_means(sum_g, sum_gx, weight_bn, count)
+    return gxhat, gxhatx, sum_gx, sum_g
+
+
+def bn_bp(x_bn, weight_bn, bias_bn, ivar, mean, dim_bn, grad_y_bn):
+    """Returns [grad_x_bn, grad_weight_bn, grad_bias_bn]. Reference: snn.cpp:293-303 -> snn_kernel_bp.cu:288-345."""
+    return list(_bn_backward(x_bn, grad_y_bn, weight_bn, bias_bn, ivar, mean, (0.0, 0.0, 0.0, 0.0), False))
+
+
+def bn_fire_bp(spatial, weight_bn, bias_bn, ivar, mean, dim_bn, grad_spike, alpha, thresh, beta, interval):
+    """Returns [grad_spatial, grad_weight_bn, grad_bias_bn]. Reference: snn.cpp:373-387 -> snn_kernel_bp.cu:679-750."""
+    return list(_bn_backward(spatial, grad_spike, weight_bn, bias_bn, ivar, mean,
+                             (alpha, thresh, beta, interval), True))
+
+
+def bn_bp_dist1(x_bn, weight_bn, bias_bn, ivar, mean, dim_bn, grad_y_bn):
+    """Returns [local_grad_xhat, local_grad_xhatx, grad_weight_bn, grad_bias_bn]. Reference: snn.cpp:317-327 -> snn_kernel_bp.cu:348-392."""
+    return list(_bn_backward_local(x_bn, grad_y_bn, weight_bn, bias_bn, ivar, mean, (0.0, 0.0, 0.0, 0.0), False))
+
+
+def bn_bp_dist2(x_bn, weight_bn, bias_bn, ivar, mean, dim_bn, grad_y_bn, grad_xhat, grad_xhatx):
+    """Returns grad_x_bn from all-reduced channel means. Reference: snn.cpp:343-355 -> snn_kernel_bp.cu:394-425."""
+    return _capi.bn_lif_bwd_input(x_bn, grad_y_bn, weight_bn, bias_bn, ivar, mean, grad_xhat, grad_xhatx,
+                                  0.0, 0.0, 0.0, 0.0, fire=False)
+
+
+def bn_fire_bp_dist1(spatial, weight_bn, bias_bn, ivar, mean, dim_bn, grad_spike, alpha, thresh, beta, interval):
+    """Returns [local_grad_xhat, local_grad_xhatx, grad_weight_bn, grad_bias_bn]. Reference: snn.cpp:405-421 -> snn_kernel_bp.cu:753-806."""
+    return list(_bn_backward_local(spatial, grad_spike, weight_bn, bias_bn, ivar, mean,
+                                   (alpha, thresh, beta, interval), True))
+
+
+def bn_fire_bp_dist2(spatial, weight_bn, bias_bn, ivar, mean, grad_spike, grad_xhat, grad_xhatx,
+                     alpha, thresh, beta, interval):
+    """Returns grad_spatial from all-reduced channel means. Reference: snn.cpp:442-460 -> snn_kernel_bp.cu:808-854."""
+    return _capi.bn_lif_bwd_input(spatial, grad_spike, weight_bn, bias_bn, ivar, mean, grad_xhat,
+                                  grad_xhatx, alpha, thresh, beta, interval, fire=True)
+
+
+def _bn_spikes_again(spatial, weight_bn, bias_bn, ivar, mean, alpha, thresh):
+    """Spikes rebuilt at backward time with w' = weight*ivar (reference: bn_fire_us_fp_kernel,
+    snn_kernel_bp.cu:481-530); only the spikes are materialised, they are a GEMM / conv operand."""
+    return _capi.bn_lif_fwd(spatial, weight_bn, bias_bn, None, mean, 0.0, alpha, thresh, ivar=ivar)[1]
+
+
+def bn_fire_fc_fp(spatial, weight_bn, bias_bn, var, mean, eps_bn, weight_fc, bias_fc, alpha, thresh):
+    """Returns [ivar, fc]. Reference: snn.cpp:85-101 -> snn_kernel_fp.cu:244-291."""
+    ivar, spike = bn_fire_s_fp(spatial, weight_bn, bias_bn, var, mean, eps_bn, alpha, thresh)
+    return [ivar, fc_fp(spike, weight_fc, bias_fc)]
+
+
+def bn_fire_fc_bp(spatial, weight_bn, bias_bn, ivar, mean, dim_bn, grad_fc, weight_fc, bias_fc, dim_fc,
+                  alpha, thresh, beta, interval):
+    """Returns [grad_spatial, grad_weight_bn, grad_bias_bn, grad_weight_fc, grad_bias_fc]. Reference: snn.cpp:484-504 -> snn_kernel_bp.cu:860-962."""
+    spike = _bn_spikes_again(spatial, weight_bn, bias_bn, ivar, mean, alpha, thresh)
+    grad_spike, grad_w, grad_b = _fc_grads(_rows(spike), grad_fc, weight_fc, dim_fc)
+    gx, gwb, gbb = _bn_backward(spatial, grad_spike.view(spatial.shape), weight_bn, bias_bn, ivar, mean,
+                                (alpha, thresh, beta, interval), True)
+    return [gx, gwb, gbb, grad_w, grad_b]
+
+
+def bn_fire_fc_bp_dist1(spatial, weight_bn, bias_bn, ivar, mean, dim_bn, grad_fc, weight_fc, bias_fc,
+                        dim_fc, alpha, thresh, beta, interval):
+    """Returns [grad_spike, local_grad_xhat, local_grad_xhatx, grad_weight_bn, grad_bias_bn, grad_weight_fc, grad_bias_fc]. Reference: snn.cpp:528-551 -> snn_kernel_bp.cu:966-1061."""
+    spike = _bn_spikes_again(spatial, weight_bn, bias_bn, ivar, mean, alpha, thresh)
+    grad_spike, grad_w, grad_b = _fc_grads(_rows(spike), grad_fc, weight_fc, dim_fc)
+    grad_spike = grad_spike.view(spatial.shape)
+    gxhat, gxhatx, gwb, gbb = _bn_backward_local(spatial, grad_spike, weight_bn, bias_bn, ivar, mean,
+                                                 (alpha, thresh, beta, interval), True)
+    return [grad_spike, gxhat, gxhatx, gwb, gbb, grad_w, grad_b]
+
+
+def bn_fire_conv_fp(spatial, weight_bn, bias_bn, var, mean, eps_bn, weight_conv, bias_conv, stride,
+                    padding, dilation, groups, benchmark, deterministic, alpha, thresh):
+    """Returns [ivar, conv]. Reference: snn.cpp:162-187 -> snn_kernel_fp.cu:361-410."""
+    ivar, spike = bn_fire_s_fp(spatial, weight_bn, bias_bn, var, mean, eps_bn, alpha, thresh)
+    return [ivar, conv_fp(spike, weight_conv, bias_conv, stride, padding, dilation, groups, benchmark,
+                          deterministic)]
+
+
+def bn_fire_conv_bp(spatial, weight_bn, bias_bn, ivar, mean, dim_bn, grad_conv, weight_conv, stride,
+                    padding, dilation, groups, benchmark, deterministic, allow_tf32, dim_conv,
+                    alpha, thresh, beta, interval):
+    """Returns [grad_spatial, grad_weight_bn, grad_bias_bn, grad_weight_conv, grad_bias_conv]. Reference: snn.cpp:630-658 -> snn_kernel_bp.cu:1180-1262."""
+    spike = _bn_spikes_again(spatial, weight_bn, bias_bn, ivar, mean, alpha, thresh)
+    grad_spike, grad_w, grad_b = _conv_grads(spike, grad_conv, weight_conv, stride, padding, dilation,
+                                             groups, dim_conv)
+    gx, gwb, gbb = _bn_backward(spatial, grad_spike.view(spatial.shape), weight_bn, bias_bn, ivar, mean,
+                                (alpha, thresh, beta, interval), True)
+    return [gx, gwb, gbb, grad_w, grad_b]
+
+
+def bn_fire_conv_bp_dist1(spatial, weight_bn, bias_bn, ivar, mean, dim_bn, grad_conv, weight_conv, stride,
+                          padding, dilation, groups, benchmark, deterministic, allow_tf32, dim_conv,
+                          alpha, thresh, beta, interval):
+    """Returns [grad_spike, local_grad_xhat, local_grad_xhatx, grad_weight_bn, grad_bias_bn, grad_weight_conv, grad_bias_conv]. Reference: snn.cpp:687-716 -> snn_kernel_bp.cu:1265-1340."""
+    spike = _bn_spikes_again(spatial, weight_bn, bias_bn, ivar, mean, alpha, thresh)
+    grad_spike, grad_w, grad_b = _conv_grads(spike, grad_conv, weight_conv, stride, padding, dilation,
+                                             groups, dim_conv)
+    grad_spike = grad_spike.view(spatial.shape)
+    gxhat, gxhatx, gwb, gbb = _bn_backward_local(spatial, grad_spike, weight_bn, bias_bn, ivar, mean,
+                                                 (alpha, thresh, beta, interval), True)
+    return [grad_spike, gxhat, gxhatx, gwb, gbb, grad_w, grad_b]

@@ -48,6 +48,129 @@ def ce_head_case(gop, x, labels):
     return u.detach().numpy(), s.detach().numpy(), xr.grad.numpy(), out.detach().numpy(), float(loss.detach())
 
 
+def make_bn_golden(gop):
+    """Batch-norm family: the reference's gold modules in training mode (batch statistics), as its
+    test_bn.py / test_bn_fire.py / test_bn_fire_fc.py / test_bn_fire_conv.py use them. Seeds are
+    advanced until no membrane potential lies within 1e-4 of the threshold, so the comparison
+    does not hinge on how the normalisation happens to round."""
+    gop.time_step = 6
+    out = {}
+    shapes = {"fc": (6, 2, 8), "conv": (6, 2, 8, 8, 8)}
+
+    def stats(x, kind):
+        dims = (0, 1) if kind == "fc" else (0, 1, 3, 4)
+        var, mean = torch.var_mean(x, dim=dims, unbiased=False)
+        return var.numpy(), mean.numpy()
+
+    def randomise(bn, gen):
+        w = 0.5 + torch.rand(bn.num_features, generator=gen)
+        b = 0.3 * torch.randn(bn.num_features, generator=gen)
+        bn.weight = torch.nn.Parameter(w.clone())
+        bn.bias = torch.nn.Parameter(b.clone())
+        return w.numpy(), b.numpy()
+
+    for kind, shape in shapes.items():
+        # plain BN
+        gen = torch.Generator().manual_seed(31)
+        mod = gop.Bn(8, kind)
+        w, b = randomise(mod.bn, gen)
+        x = torch.randn(shape, generator=gen)
+        xr = x.clone().requires_grad_(True)
+        y = mod(xr)
+        gy = torch.randn(y.shape, generator=gen)
+        y.backward(gy)
+        k = f"bn_{kind}"
+        out[f"{k}_x"], out[f"{k}_w"], out[f"{k}_b"], out[f"{k}_y"], out[f"{k}_gy"] = x.numpy(), w, b, y.detach().numpy(), gy.numpy()
+        out[f"{k}_gx"], out[f"{k}_gw"], out[f"{k}_gb"] = xr.grad.numpy(), mod.bn.weight.grad.numpy(), mod.bn.bias.grad.numpy()
+        out[f"{k}_var"], out[f"{k}_mean"] = stats(x, kind)
+
+        # BN folded into LIF
+        seed = 40
+        while True:
+            gen = torch.Generator().manual_seed(seed)
+            mod = gop.BnFire(8, kind)
+            w, b = randomise(mod.bn, gen)
+            x = torch.randn(shape, generator=gen)
+            xr = x.clone().requires_grad_(True)
+            u, s = mod(xr)
+            if float((u.detach() - gop.thresh).abs().min()) > 1e-4:
+                break
+            seed += 1
+        g = torch.randn(s.shape, generator=gen)
+        s.backward(g)
+        k = f"bnfire_{kind}"
+        out[f"{k}_x"], out[f"{k}_w"], out[f"{k}_b"], out[f"{k}_g"] = x.numpy(), w, b, g.numpy()
+        out[f"{k}_u"], out[f"{k}_s"] = u.detach().numpy(), s.detach().numpy()
+        out[f"{k}_gx"], out[f"{k}_gw"], out[f"{k}_gb"] = xr.grad.numpy(), mod.bn.weight.grad.numpy(), mod.bn.bias.grad.numpy()
+        out[f"{k}_var"], out[f"{k}_mean"] = stats(x, kind)
+
+        # BN + LIF + fc  /  BN + LIF + conv
+        for comp in (("fc",) if kind == "fc" else ("fc", "conv")):
+            seed = 60
+            while True:
+                torch.manual_seed(seed)
+                gen = torch.Generator().manual_seed(seed)
+                if comp == "fc":
+                    # as test_bn_fire_fc.py does: BN over 8 channels, then the fc weight is
+                    # replaced by one that matches the flattened input (8*8*8 = 512 for images)
+                    mod = gop.BnFireFc(8, 8, bn_fire=True, bn_layer_type=kind)
+                    if kind == "conv":
+                        mod.fc.weight = torch.nn.Parameter(0.05 * torch.randn(8, 512))
+                    lin_w, lin_b = mod.fc.weight, mod.fc.bias
+                else:
+                    mod = gop.BnFireConv(8, 8, bn_fire=True)
+                    lin_w, lin_b = mod.conv.weight, mod.conv.bias
+                w, b = randomise(mod.bn, gen)
+                x = torch.randn(shape, generator=gen)
+                with torch.no_grad():
+                    u, _ = gop.gold_bn_fire(x, mod.bn)
+                mod.bn.reset_running_stats()
+                if float((u - gop.thresh).abs().min()) > 1e-4:
+                    break
+                seed += 1
+            xr = x.clone().requires_grad_(True)
+            y = mod(xr)
+            gy = torch.randn(y.shape, generator=gen)
+            y.backward(gy)
+            k = f"bnfire{comp}_{kind}"
+            out[f"{k}_x"], out[f"{k}_w"], out[f"{k}_b"] = x.numpy(), w, b
+            out[f"{k}_lw"], out[f"{k}_lb"] = lin_w.detach().numpy().copy(), lin_b.detach().numpy().copy()
+            out[f"{k}_y"], out[f"{k}_gy"], out[f"{k}_gx"] = y.detach().numpy(), gy.numpy(), xr.grad.numpy()
+            out[f"{k}_gw"], out[f"{k}_gb"] = mod.bn.weight.grad.numpy(), mod.bn.bias.grad.numpy()
+            out[f"{k}_glw"], out[f"{k}_glb"] = lin_w.grad.numpy(), lin_b.grad.numpy()
+            out[f"{k}_var"], out[f"{k}_mean"] = stats(x, kind)
+    np.savez_compressed(os.path.join(HERE, "bn_golden.npz"), **out)
+
+
+def record_reference_model_layouts(ref_root):
+    """Parameter names and shapes of the reference's own networks (snnlib/example/models.py),
+    built from the reference's class definitions. Its modules import a compiled ``snnlib``; the
+    constructors never call into it, so this repository's package is aliased under that name just
+    to let the import succeed."""
+    import importlib
+    import json
+    root = os.path.dirname(os.path.dirname(HERE))
+    sys.path.insert(0, root)
+    import snn_gpu_training_bptt_b200 as pkg
+    from snn_gpu_training_bptt_b200 import snnlib as native
+    saved = {k: sys.modules.get(k) for k in ("snnlib", "snnlib_func", "snnlib_op", "models")}
+    for k in ("snnlib_func", "snnlib_op", "models"):
+        sys.modules.pop(k, None)
+    sys.modules["snnlib"] = native                # only the compiled module is substituted;
+    ref_models = importlib.import_module("models")  # snnlib_func / snnlib_op / models are the reference's files
+    assert ref_models.__file__.startswith(ref_root)
+    layouts = {}
+    for name in ("CIFAR_BN", "Alexnet_BN_DIST", "Resnet_DIST"):
+        sd = getattr(ref_models, name)().state_dict()
+        layouts[name] = {k: list(v.shape) for k, v in sd.items()}
+    with open(os.path.join(HERE, "reference_model_layouts.json"), "w") as f:
+        json.dump(layouts, f, indent=0, sort_keys=True)
+    for k, v in saved.items():
+        sys.modules.pop(k, None)
+        if v is not None:
+            sys.modules[k] = v
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--ref", default="/root/reference")
@@ -127,6 +250,8 @@ def main():
             out[f"{k}_gb"] = mod.fc.bias.grad.numpy()
 
     np.savez_compressed(os.path.join(HERE, "lif_golden.npz"), **out)
+    make_bn_golden(gop)
+    record_reference_model_layouts(args.ref)
 
     # ---- 5. the full single-layer case: T=8, [32,128,16,16], seed 1234 ---------------------
     # Too large to store; keep digests of inputs and outputs plus a strided sample.

@@ -101,3 +101,17 @@ def test_time_major_dense_detection():
     assert not dense(x[:, :, :, :, ::2]) and not dense(x[::2]) and not dense(x.transpose(0, 1))
     cl = torch.zeros(24, 8, 5, 5).to(memory_format=torch.channels_last).view(6, 4, 8, 5, 5)
     assert dense(cl) and torch.empty_like(cl).stride() == cl.stride()
+
+
+def test_reference_networks_keep_their_state_dict_layout():
+    """CIFAR_BN / Alexnet_BN_DIST / Resnet_DIST expose exactly the parameter names and shapes of
+    the reference's classes (recorded from the reference's models.py by tests/golden/make_golden.py),
+    so checkpoints interchange."""
+    import json
+    import os
+    here = os.path.dirname(os.path.abspath(__file__))
+    with open(os.path.join(here, "golden", "reference_model_layouts.json")) as f:
+        layouts = json.load(f)
+    for name, want in layouts.items():
+        sd = getattr(models, name)().state_dict()
+        assert {k: list(v.shape) for k, v in sd.items()} == want, name

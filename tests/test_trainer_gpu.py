@@ -145,3 +145,37 @@ def test_nccl_data_parallel_matches_single_process(tmp_path):
     for name in single:
         assert torch.equal(r0[name], r1[name]), name
         assert_grad_close(r0[name], single[name], rtol=2e-3, atol=2e-5, what=name)
+
+
+def test_reference_cifar_bn_network_trains_and_evaluates():
+    """The reference's own CIFAR network (all layers BN-fused) through two SGD steps, then in
+    evaluation mode with running statistics (train_test_cifar.py:52-92)."""
+    from snn_gpu_training_bptt_b200 import snnlib_func as sf
+    from snn_gpu_training_bptt_b200.example import models
+    old_T = sf.time_step
+    try:
+        sf.time_step = 4
+        torch.manual_seed(0)
+        net = models.CIFAR_BN().cuda()
+        opt = torch.optim.SGD(net.parameters(), lr=1e-2, momentum=0.9)
+        images = torch.rand(4, 3, 32, 32, device="cuda")
+        labels = torch.tensor([1, 2, 3, 4], device="cuda")
+        net.set_bn(True)
+        before = net.conv2_1.running_mean.clone()
+        losses = []
+        for _ in range(2):
+            net.zero_grad()
+            opt.zero_grad()
+            loss = F.cross_entropy(net(images), labels)
+            loss.backward()
+            opt.step()
+            losses.append(float(loss.detach()))
+        assert all(np.isfinite(v) for v in losses)
+        assert not torch.equal(before, net.conv2_1.running_mean)
+        assert all(p.grad is not None and torch.isfinite(p.grad).all() for p in net.parameters() if p.requires_grad)
+        net.set_bn(False)
+        with torch.no_grad():
+            out = net(images)
+        assert out.shape == (4, 10) and torch.isfinite(out).all()
+    finally:
+        sf.time_step = old_T
