@@ -356,6 +356,139 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+# ----------------------------------------------------------------------------------------------
+# secondary workloads (not the contract line): bandwidth sweep, BN-fused LIF, linear + LIF
+# ----------------------------------------------------------------------------------------------
+def _time_kernel(fn, reps, flush=None):
+    """Median device time of fn() in ms over `reps` launches (CUDA events on the current stream).
+    `flush` (a large tensor) is rewritten before each launch when the working set fits in L2."""
+    import torch
+    for _ in range(3):
+        fn()
+    times = []
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    for _ in range(reps):
+        if flush is not None:
+            flush.zero_()
+        e0.record()
+        fn()
+        e1.record()
+        e1.synchronize()
+        times.append(e0.elapsed_time(e1))
+    return statistics.median(times)
+
+
+def run_sweep(args):
+    """Single-GPU bandwidth sweep: T in {4,8,16} x N in {2^20,2^22,2^24,2^26}, fp32 and bf16 I/O."""
+    import torch
+    from snn_gpu_training_bptt_b200 import _capi
+    peak, peak_src = measured_peak()
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    for dtype, name, es in ((torch.float32, "f32", 4), (torch.bfloat16, "bf16", 2)):
+        for T in (4, 8, 16):
+            for lg in (20, 22, 24, 26):
+                N = 1 << lg
+                gen = torch.Generator(device=dev).manual_seed(1234)
+                x = (torch.randn((T, 1, N), device=dev, generator=gen) + 0.5).to(dtype)
+                g = torch.randn((T, 1, N), device=dev, generator=gen).to(dtype)
+                s, gx = torch.empty_like(x), torch.empty_like(x)
+                L, sp = _capi.lib(), _capi._stream(dev)
+                code = _capi.DTYPE_CODE[dtype]
+                px, pg, ps, pgx = (_capi._ptr(t) for t in (x, g, s, gx))
+                fwd = lambda: L.snn_lif_fwd(px, ps, None, None, T, N, code, ALPHA, THRESH, sp)
+                bwd = lambda: L.snn_lif_bwd(px, pg, pgx, T, N, code, ALPHA, THRESH, BETA, INTERVAL, None, 0, sp)
+                small = 4 * T * N * es < (512 << 20)
+                t_f = _time_kernel(fwd, 20, flush if small else None)
+                t_b = _time_kernel(bwd, 20, flush if small else None)
+                gb = lambda nbytes, ms: nbytes * T * N / ms / 1e6
+                tot = gb(5 * es, t_f + t_b)
+                print(json.dumps({
+                    "metric": "lif_fwd_bwd_hbm_gbps", "value": round(tot, 1), "unit": "GB/s", "dtype": name,
+                    "config": {"workload": f"lif sweep {name} T={T} N=2^{lg}",
+                               "l2": "flushed between launches" if small else "working set > L2"},
+                    "fwd_ms": round(t_f, 4), "fwd_gbs": round(gb(2 * es, t_f), 1),
+                    "bwd_ms": round(t_b, 4), "bwd_gbs": round(gb(3 * es, t_b), 1),
+                    "frac_of_peak": round(tot / peak, 4), "peak": peak, "peak_source": peak_src}))
+                del x, g, s, gx
+
+
+def run_bn_lif(args):
+    """BN-fused LIF forward + two-pass backward, fp32, [T=8, B=256, C=256, 32x32] (N = 2^26)."""
+    import torch
+    from snn_gpu_training_bptt_b200 import _capi
+    peak, peak_src = measured_peak()
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    T, B, C, HW = 8, 256 >> (26 - args.log2n), 256, 1024
+    N = B * C * HW
+    gen = torch.Generator(device=dev).manual_seed(1234)
+    x = torch.randn((T, B, C, 32, 32), device=dev, generator=gen) * 1.5 + 0.3
+    g = torch.randn((T, B, C, 32, 32), device=dev, generator=gen)
+    w = torch.rand(C, device=dev, generator=gen) + 0.5
+    b = torch.randn(C, device=dev, generator=gen) * 0.2
+    var, mean = torch.var_mean(x, dim=(0, 1, 3, 4), unbiased=False)
+    L, sp = _capi.lib(), _capi._stream(dev)
+    out, gx = torch.empty_like(x), torch.empty_like(x)
+    ivar = torch.empty_like(w)
+    sums = torch.empty((2, C), device=dev)
+    means = torch.empty((2, C), device=dev)
+    P = _capi._ptr
+    fwd = lambda: L.snn_bn_lif_fwd(P(x), P(w), P(b), P(var), P(mean), 1e-5, P(out), None, P(ivar), T, N, C, HW, 0, 1,
+                                   ALPHA, THRESH, sp)
+    assert fwd() == 0
+    def bwd():
+        rc = L.snn_bn_lif_bwd_sums(P(x), P(g), P(w), P(b), P(ivar), P(mean), P(sums[0]), P(sums[1]), T, N, C, HW, 0, 1,
+                                   ALPHA, THRESH, BETA, INTERVAL, sp)
+        rc |= L.snn_bn_channel_means(P(sums[0]), P(sums[1]), P(w), P(means[0]), P(means[1]), C, float(T * N // C), sp)
+        rc |= L.snn_bn_lif_bwd_input(P(x), P(g), P(w), P(b), P(ivar), P(mean), P(means[0]), P(means[1]), P(gx), T, N, C,
+                                     HW, 0, 1, ALPHA, THRESH, BETA, INTERVAL, sp)
+        assert rc == 0
+    t_f = _time_kernel(fwd, args.steps if args.steps < 50 else 20)
+    t_b = _time_kernel(bwd, args.steps if args.steps < 50 else 20)
+    gb = lambda nbytes, ms: nbytes * T * N / ms / 1e6
+    print(json.dumps({
+        "metric": "bn_lif_fwd_bwd_hbm_gbps", "value": round(gb(28, t_f + t_b), 1), "unit": "GB/s", "dtype": "f32",
+        "config": {"workload": f"bn_fire fwd + 2-pass bwd fp32 T=8 [B={B},C=256,32x32] N=2^{args.log2n}",
+                   "bytes_per_neuron_step": "fwd 8, bwd sums pass 8 + input pass 12",
+                   "l2": "working set > L2"},
+        "fwd_ms": round(t_f, 4), "fwd_gbs": round(gb(8, t_f), 1), "bwd_ms": round(t_b, 4),
+        "bwd_gbs": round(gb(20, t_b), 1), "frac_of_peak": round(gb(28, t_f + t_b) / peak, 4), "peak": peak,
+        "peak_source": peak_src,
+        "reference_traffic_bytes_per_neuron_step": "8 fwd + 8 (u rebuild) + 12 (sums) + 16 (input grad) = 44"}))
+
+
+def run_linear_lif(args):
+    """Synaptic linear followed by LIF (T=8, batch 256, 2048 -> 2048), forward + BPTT backward with
+    weight, bias and input gradients; Bernoulli(0.2) input spikes, Kaiming-uniform weights."""
+    import torch
+    from snn_gpu_training_bptt_b200 import snnlib_func as sf
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    T, B, K, M = 8, 256, 2048, 2048
+    torch.manual_seed(1234)
+    lin = torch.nn.Linear(K, M).to(dev)
+    flops = 2.0 * T * B * K * M * 3
+    for dtype, name in ((torch.float32, "fp32 (TF32 off)"), (torch.bfloat16, "bf16")):
+        torch.backends.cuda.matmul.allow_tf32 = False
+        x = (torch.rand((T, B, K), device=dev) < 0.2).to(dtype).requires_grad_(True)
+        w = lin.weight.detach().clone().requires_grad_(True)
+        bias = lin.bias.detach().clone().requires_grad_(True)
+        gs = torch.randn((T, B, M), device=dev).to(dtype)
+
+        def step():
+            x.grad = w.grad = bias.grad = None
+            s = sf.fire_func(sf.fc_func(x, w, bias))
+            s.backward(gs)
+        ms = _time_kernel(step, 20)
+        print(json.dumps({
+            "metric": "linear_lif_fwd_bwd_tflops", "value": round(flops / ms / 1e9, 1), "unit": "TFLOP/s",
+            "dtype": name, "ms_per_step": round(ms, 4),
+            "config": {"workload": "fc 2048->2048 + LIF, T=8, batch 256, fwd + BPTT bwd (dX, dW, db)",
+                       "path": "one cuBLAS GEMM over the merged T*B rows + snn_lif_fwd / snn_lif_bwd"}}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -368,9 +501,17 @@ def main():
     ap.add_argument("--trainer-steps", type=int, default=30)
     ap.add_argument("--log2n", type=int, default=26,
                     help="log2 of neurons per GPU (26 = the benchmark size; smaller only for profiler captures)")
+    ap.add_argument("--workload", default="lif", choices=["lif", "sweep", "bn_lif", "linear_lif"],
+                    help="lif = the benchmark line; the others are secondary single-GPU measurements")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference_arm(args)
+    elif args.workload == "sweep":
+        run_sweep(args)
+    elif args.workload == "bn_lif":
+        run_bn_lif(args)
+    elif args.workload == "linear_lif":
+        run_linear_lif(args)
     else:
         run_ours(args)
 

@@ -166,6 +166,36 @@ int snn_bn_lif_bwd_input(const void *x, const void *grad, const float *weight, c
                          int64_t inner, int dtype, int fire, float alpha, float thresh, float beta,
                          float interval, void *stream);
 
+/* ----------------------------------------------------------------------------------------
+ * LIF followed by AvgPool2d(2) on every time step, fused. No counterpart in the reference's
+ * native table: its models place `Fire` in front of pooling-free strided convolutions, while the
+ * VGG-style benchmark network pools after LIF (torch AvgPool2d per time step). Fusing keeps the
+ * full-resolution spikes and their gradient out of HBM.
+ * x is [T][B][H][W][C] in memory (channels-last images), outputs [T][B][H/2][W/2][C];
+ * H and W even, T <= 16, dtype f32 / bf16 / f16.
+ *   forward   out = mean over each 2x2 window of the LIF spikes of x        (values k/4, exact)
+ *   backward  grad_x = LIF reverse pass with upstream gradient grad_out/4 at each window position
+ * -------------------------------------------------------------------------------------- */
+int snn_lif_pool_fwd(const void *x, void *out, int64_t T, int64_t B, int64_t H, int64_t W,
+                     int64_t C, int dtype, float alpha, float thresh, void *stream);
+int snn_lif_pool_bwd(const void *x, const void *grad_out, void *grad_x, int64_t T, int64_t B,
+                     int64_t H, int64_t W, int64_t C, int dtype, float alpha, float thresh,
+                     float beta, float interval, void *stream);
+
+/* ----------------------------------------------------------------------------------------
+ * Per-channel bias of a synaptic layer. Element (o, c, i) at (o*C + c)*inner + i: inner = 1 for
+ * channels-last images and [rows, C] matrices, inner = H*W for contiguous [N, C, H, W].
+ *   snn_channel_bias_add   y[o, c, i] += bias[c], in place
+ *   snn_channel_sum        out[c] = sum over o, i of grad[o, c, i]   (out is zeroed by the call)
+ * They stand in for the bias handling inside the reference's per-time-step at::linear /
+ * at::cudnn_convolution calls (snnlib/cuda/snn_kernel_fp.cu:346-352, :445) and for its
+ * at::sum(grad, dims) bias gradients (snnlib/cuda/snn_kernel_bp.cu:1127, :1172, :1401, :1435).
+ * -------------------------------------------------------------------------------------- */
+int snn_channel_bias_add(void *y, const float *bias, int64_t outer, int64_t C, int64_t inner,
+                         int dtype, void *stream);
+int snn_channel_sum(const void *grad, float *out, int64_t outer, int64_t C, int64_t inner,
+                    int dtype, void *stream);
+
 /*
  * LIF backward through time for callers that may not allocate device memory.
  *

@@ -28,6 +28,10 @@ SIGNATURES = {
     "snn_lif_bwd": (_int, [_vp, _vp, _vp, _i64, _i64, _int, _f32, _f32, _f32, _f32, _vp, _sz, _vp]),
     "snn_spike_unpack": (_int, [_vp, _vp, _i64, _i64, _int, _vp]),
     "snn_lif_bwd_noalloc": (_int, [_vp, _vp, _vp, _i64, _i64, _int, _f32, _f32, _f32, _f32, _vp]),
+    "snn_lif_pool_fwd": (_int, [_vp, _vp, _i64, _i64, _i64, _i64, _i64, _int, _f32, _f32, _vp]),
+    "snn_lif_pool_bwd": (_int, [_vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _int, _f32, _f32, _f32, _f32, _vp]),
+    "snn_channel_bias_add": (_int, [_vp, _vp, _i64, _i64, _i64, _int, _vp]),
+    "snn_channel_sum": (_int, [_vp, _vp, _i64, _i64, _i64, _int, _vp]),
     "snn_bn_lif_fwd": (_int, [_vp, _vp, _vp, _vp, _vp, _f32, _vp, _vp, _vp, _i64, _i64, _i64, _i64,
                               _int, _int, _f32, _f32, _vp]),
     "snn_bn_lif_bwd_sums": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64,
@@ -316,3 +320,90 @@ def bn_lif_bwd_input(x, grad, weight, bias, ivar, mean, gxhat, gxhatx, alpha, th
                                         _stream(x.device))
     check("snn_bn_lif_bwd_input", rc)
     return gx
+
+
+# ----------------------------------------------------------------------------------------------
+# LIF + 2x2 average pool, fused (channels-last images)
+# ----------------------------------------------------------------------------------------------
+def _channels_last_5d(x):
+    """[T, B, C, H, W] tensor whose memory order is (T, B, H, W, C); copies only if it is not."""
+    T, B, C, H, W = x.shape
+    want = (B * H * W * C, H * W * C, 1, W * C, C)
+    if tuple(x.stride()) == want:
+        return x
+    out = torch.empty_strided(x.shape, want, dtype=x.dtype, device=x.device)
+    out.copy_(x)
+    return out
+
+
+def lif_pool_fwd(x, alpha, thresh):
+    """Pooled spikes [T, B, C, H/2, W/2] (channels-last memory order) of the LIF of x."""
+    _require_cuda(x, "spatial")
+    if x.dim() != 5 or x.shape[3] % 2 or x.shape[4] % 2:
+        raise ValueError("fused LIF+pool needs [T, B, C, H, W] with even H and W")
+    x = _channels_last_5d(x)
+    T, B, C, H, W = x.shape
+    with torch.cuda.device(x.device):
+        out = torch.empty_strided((T, B, C, H // 2, W // 2),
+                                  (B * (H // 2) * (W // 2) * C, (H // 2) * (W // 2) * C, 1, (W // 2) * C, C),
+                                  dtype=x.dtype, device=x.device)
+        rc = lib().snn_lif_pool_fwd(_ptr(x), _ptr(out), T, B, H, W, C, DTYPE_CODE[x.dtype], float(alpha),
+                                    float(thresh), _stream(x.device))
+    check("snn_lif_pool_fwd", rc)
+    return x, out
+
+
+def lif_pool_bwd(x, grad_out, alpha, thresh, beta, interval):
+    """grad w.r.t. x (channels-last, as produced by lif_pool_fwd's first return value)."""
+    T, B, C, H, W = x.shape
+    g = _channels_last_5d(grad_out)
+    with torch.cuda.device(x.device):
+        gx = torch.empty_like(x)
+        rc = lib().snn_lif_pool_bwd(_ptr(x), _ptr(g), _ptr(gx), T, B, H, W, C, DTYPE_CODE[x.dtype],
+                                    float(alpha), float(thresh), float(beta), float(interval), _stream(x.device))
+    check("snn_lif_pool_bwd", rc)
+    return gx
+
+
+# ----------------------------------------------------------------------------------------------
+# per-channel bias add / bias-gradient sum for [N, C, ...] activations (dim 1 = channels)
+# ----------------------------------------------------------------------------------------------
+def _channel_geometry(t):
+    """(outer, C, inner) if ``t`` ([N, C, ...]) is laid out as (o*C + c)*inner + i, else None."""
+    C = t.shape[1]
+    if t.numel() == 0:
+        return 0, C, 1
+    if t.is_contiguous():
+        inner = t.numel() // (t.shape[0] * C)
+        return t.shape[0], C, inner
+    if t.dim() == 4 and t.is_contiguous(memory_format=torch.channels_last):
+        return t.numel() // C, C, 1
+    return None
+
+
+def channel_bias_add_(y, bias):
+    """y[:, c] += bias[c] in place (y: [N, C, ...] contiguous or channels-last; bias fp32 [C])."""
+    geo = _channel_geometry(y)
+    if geo is None or y.dtype not in DTYPE_CODE or y.dtype == torch.float64 or bias.dtype != torch.float32:
+        raise TypeError("channel_bias_add_: needs a dense f32/bf16/f16 activation and an fp32 bias")
+    outer, C, inner = geo
+    with torch.cuda.device(y.device):
+        rc = lib().snn_channel_bias_add(_ptr(y), _ptr(bias.contiguous()), outer, C, inner, DTYPE_CODE[y.dtype],
+                                        _stream(y.device))
+    check("snn_channel_bias_add", rc)
+    return y
+
+
+def channel_sum(grad):
+    """fp32 [C] sums of grad ([N, C, ...]) over every axis but the channel axis."""
+    geo = _channel_geometry(grad)
+    if geo is None:
+        grad = grad.contiguous()
+        geo = _channel_geometry(grad)
+    outer, C, inner = geo
+    with torch.cuda.device(grad.device):
+        out = torch.empty(C, dtype=torch.float32, device=grad.device)
+        rc = lib().snn_channel_sum(_ptr(grad), _ptr(out), outer, C, inner, DTYPE_CODE[grad.dtype],
+                                   _stream(grad.device))
+    check("snn_channel_sum", rc)
+    return out

@@ -176,9 +176,14 @@ int snn_bn_lif_bwd_sums(const void* x, const void* grad, const float* weight, co
             with_vec4(vec, [&](auto v) {
                 constexpr int VEC = decltype(v)::value;
                 int nq; const size_t smem = smem_for(VEC, &nq);
-                snn::bn_lif_bwd_sums_kernel<IO, VEC, 2, false><<<grid_for(Ni, VEC), kBlock, smem, st>>>(
-                    static_cast<const IO*>(x), static_cast<const IO*>(grad), sum_g, sum_gx, p, Ti, Ni, nq,
-                    alpha, thresh, beta, interval);
+                if (inner % (32 * VEC) == 0)
+                    snn::bn_lif_bwd_sums_kernel<IO, VEC, 2, false, true><<<grid_for(Ni, VEC), kBlock, 0, st>>>(
+                        static_cast<const IO*>(x), static_cast<const IO*>(grad), sum_g, sum_gx, p, Ti, Ni, nq,
+                        alpha, thresh, beta, interval);
+                else
+                    snn::bn_lif_bwd_sums_kernel<IO, VEC, 2, false, false><<<grid_for(Ni, VEC), kBlock, smem, st>>>(
+                        static_cast<const IO*>(x), static_cast<const IO*>(grad), sum_g, sum_gx, p, Ti, Ni, nq,
+                        alpha, thresh, beta, interval);
             });
             return;
         }
@@ -187,9 +192,14 @@ int snn_bn_lif_bwd_sums(const void* x, const void* grad, const float* weight, co
             with_vec4(vec < max_vec<TMAX>() ? vec : max_vec<TMAX>(), [&](auto v) {
                 constexpr int VEC = decltype(v)::value < max_vec<TMAX>() ? decltype(v)::value : max_vec<TMAX>();
                 int nq; const size_t smem = smem_for(VEC, &nq);
-                snn::bn_lif_bwd_sums_kernel<IO, VEC, TMAX, true><<<grid_for(Ni, VEC), kBlock, smem, st>>>(
-                    static_cast<const IO*>(x), static_cast<const IO*>(grad), sum_g, sum_gx, p, Ti, Ni, nq,
-                    alpha, thresh, beta, interval);
+                if (inner % (32 * VEC) == 0)
+                    snn::bn_lif_bwd_sums_kernel<IO, VEC, TMAX, true, true><<<grid_for(Ni, VEC), kBlock, 0, st>>>(
+                        static_cast<const IO*>(x), static_cast<const IO*>(grad), sum_g, sum_gx, p, Ti, Ni, nq,
+                        alpha, thresh, beta, interval);
+                else
+                    snn::bn_lif_bwd_sums_kernel<IO, VEC, TMAX, true, false><<<grid_for(Ni, VEC), kBlock, smem, st>>>(
+                        static_cast<const IO*>(x), static_cast<const IO*>(grad), sum_g, sum_gx, p, Ti, Ni, nq,
+                        alpha, thresh, beta, interval);
             });
         });
     });

@@ -42,8 +42,18 @@ struct BnParams {
     int C;
 };
 
+// 64-bit integer division is emulated with ~100 instructions; every practical size fits 32 bits.
+__device__ __forceinline__ long long run_of(long long n, long long inner) {
+    if (n <= 0xffffffffLL && inner <= 0xffffffffLL)
+        return static_cast<long long>(static_cast<unsigned int>(n) / static_cast<unsigned int>(inner));
+    return n / inner;
+}
+__device__ __forceinline__ int channel_of_run(long long q, int C) {
+    if (q <= 0xffffffffLL) return static_cast<int>(static_cast<unsigned int>(q) % static_cast<unsigned int>(C));
+    return static_cast<int>(q % C);
+}
 __device__ __forceinline__ int channel_of(long long n, long long inner, int C) {
-    return static_cast<int>((n / inner) % C);
+    return channel_of_run(run_of(n, inner), C);
 }
 
 // current = ((leak + (x - m) * w) + b), operations rounded one by one, association as in
@@ -76,7 +86,8 @@ __global__ void bn_lif_fwd_kernel(const IO* __restrict__ x, IO* __restrict__ out
         b[v] = p.bias[c];
         if (p.var != nullptr) {
             w[v] = wt / sqrtf(p.var[c] + p.eps);      // IEEE division and square root
-            if (ivar_out != nullptr && (i + v) < p.inner * p.C && (i + v) % p.inner == 0)
+            if (ivar_out != nullptr && (i + v) < p.inner * p.C &&
+                run_of(i + v, p.inner) * p.inner == (i + v))
                 ivar_out[c] = w[v] / wt;
         } else {
             w[v] = mul_rn(wt, p.ivar[c]);             // backward-time rebuild: w' = weight*ivar
@@ -119,78 +130,84 @@ __global__ void bn_lif_fwd_kernel(const IO* __restrict__ x, IO* __restrict__ out
 
 // ---------------------------------------------------------------------------------------
 // Shared by both backward passes: rebuild u (w' = weight*ivar, as the reference's backward
-// does) and run the reverse-time recurrence, leaving gu[t][v] in registers.
+// does), run the reverse-time recurrence and hand each gu(t, v) to `emit` as soon as it is
+// known, so no array of gradients has to stay live beside x and u.
 // ---------------------------------------------------------------------------------------
-template <typename IO, int VEC, int TMAX, bool FIRE>
+template <typename IO, int VEC, int TMAX, bool FIRE, typename Emit>
 __device__ __forceinline__ void bn_lif_grad_current(const Pack<IO, VEC> (&xin)[TMAX],
                                                     const Pack<IO, VEC> (&gin)[TMAX], int T,
                                                     const float (&m)[VEC], const float (&wiv)[VEC],
                                                     const float (&b)[VEC], float alpha, float thresh,
-                                                    float beta, float interval,
-                                                    float (&gu_out)[TMAX][VEC])
+                                                    float beta, float interval, Emit&& emit)
 {
     if constexpr (!FIRE) {
 #pragma unroll
         for (int t = 0; t < TMAX; ++t)
             if (t < T) {
 #pragma unroll
-                for (int v = 0; v < VEC; ++v) gu_out[t][v] = Elem<IO>::load(gin[t].v[v]);
+                for (int v = 0; v < VEC; ++v) emit(t, v, Elem<IO>::load(gin[t].v[v]));
             }
     } else {
-    float u[TMAX][VEC];
-    float uu[VEC], gate[VEC];
+        float u[TMAX][VEC];
+        float uu[VEC], gate[VEC];
 #pragma unroll
-    for (int v = 0; v < VEC; ++v) { uu[v] = 0.f; gate[v] = 1.f; }
+        for (int v = 0; v < VEC; ++v) { uu[v] = 0.f; gate[v] = 1.f; }
 #pragma unroll
-    for (int t = 0; t < TMAX; ++t) {
-        if (t < T) {
+        for (int t = 0; t < TMAX; ++t) {
+            if (t < T) {
 #pragma unroll
-            for (int v = 0; v < VEC; ++v) {
-                uu[v] = bn_lif_step(uu[v], gate[v], Elem<IO>::load(xin[t].v[v]), m[v], wiv[v], b[v], alpha);
-                gate[v] = (uu[v] > thresh) ? 0.f : 1.f;
-                u[t][v] = uu[v];
+                for (int v = 0; v < VEC; ++v) {
+                    uu[v] = bn_lif_step(uu[v], gate[v], Elem<IO>::load(xin[t].v[v]), m[v], wiv[v], b[v], alpha);
+                    gate[v] = (uu[v] > thresh) ? 0.f : 1.f;
+                    u[t][v] = uu[v];
+                }
+            }
+        }
+        float gu[VEC];
+#pragma unroll
+        for (int v = 0; v < VEC; ++v) gu[v] = 0.f;
+#pragma unroll
+        for (int t = TMAX - 1; t >= 0; --t) {
+            if (t < T) {
+#pragma unroll
+                for (int v = 0; v < VEC; ++v) {
+                    const float ut = u[t][v];
+                    const float ga = mul_rn(gu[v], alpha);
+                    const bool inside = inside_window(ut, thresh, interval);
+                    float gs = 0.f;
+                    if (inside) gs = sub_rn(Elem<IO>::load(gin[t].v[v]), mul_rn(ga, ut));
+                    const float keep = (ut <= thresh) ? 1.f : 0.f;
+                    gu[v] = add_rn(mul_rn(gs, beta), mul_rn(ga, keep));
+                    emit(t, v, gu[v]);
+                }
             }
         }
     }
-    float gu[VEC];
-#pragma unroll
-    for (int v = 0; v < VEC; ++v) gu[v] = 0.f;
-#pragma unroll
-    for (int t = TMAX - 1; t >= 0; --t) {
-        if (t < T) {
-#pragma unroll
-            for (int v = 0; v < VEC; ++v) {
-                const float ut = u[t][v];
-                const float ga = mul_rn(gu[v], alpha);
-                const bool inside = (sub_rn(ut, thresh) < interval) && (sub_rn(thresh, ut) < interval);
-                float gs = 0.f;
-                if (inside) gs = sub_rn(Elem<IO>::load(gin[t].v[v]), mul_rn(ga, ut));
-                const float keep = (ut <= thresh) ? 1.f : 0.f;
-                gu[v] = add_rn(mul_rn(gs, beta), mul_rn(ga, keep));
-                gu_out[t][v] = gu[v];
-            }
-        }
-    }
-    }  // FIRE
 }
 
 // ---------------------------------------------------------------------------------------
 // Backward pass 1: per-channel sums  sum_g[c] += gu ,  sum_gx[c] += gu * xhat.
-// sums must be zero before the launch. Dynamic shared memory: 2 * nq floats, nq = number of
-// distinct channel runs a CTA can touch (host computes (span + inner - 1)/inner + 1).
+// sums must be zero before the launch.
+//   WARP_RUN = true : every warp lies inside one channel run (inner % (32*VEC) == 0): warp
+//                     butterfly, then one global atomicAdd pair per warp; no shared memory.
+//   WARP_RUN = false: shared-memory accumulators, one slot per channel run a CTA can touch
+//                     (dynamic shared memory 2*nq floats, nq = (span + inner - 1)/inner + 1),
+//                     then one global atomicAdd pair per (CTA, run).
 // ---------------------------------------------------------------------------------------
-template <typename IO, int VEC, int TMAX, bool FIRE>
-__global__ void bn_lif_bwd_sums_kernel(const IO* __restrict__ x, const IO* __restrict__ g,
+template <typename IO, int VEC, int TMAX, bool FIRE, bool WARP_RUN>
+__global__ void __launch_bounds__(256, (VEC * TMAX <= 16) ? 4 : 1) bn_lif_bwd_sums_kernel(const IO* __restrict__ x, const IO* __restrict__ g,
                                        float* __restrict__ sum_g, float* __restrict__ sum_gx,
                                        BnParams p, int T, long long N, int nq, float alpha,
                                        float thresh, float beta, float interval)
 {
-    extern __shared__ float sacc[];                       // [2][nq]
-    for (int j = threadIdx.x; j < 2 * nq; j += blockDim.x) sacc[j] = 0.f;
-    __syncthreads();
+    extern __shared__ float sacc[];                       // [2][nq]   (unused when WARP_RUN)
+    if (!WARP_RUN) {
+        for (int j = threadIdx.x; j < 2 * nq; j += blockDim.x) sacc[j] = 0.f;
+        __syncthreads();
+    }
 
     const long long blk0 = static_cast<long long>(blockIdx.x) * blockDim.x * VEC;
-    const long long q0 = blk0 / p.inner;
+    const long long q0 = run_of(blk0, p.inner);
     const long long i = blk0 + static_cast<long long>(threadIdx.x) * VEC;
     const bool active = i < N;
 
@@ -203,8 +220,8 @@ __global__ void bn_lif_bwd_sums_kernel(const IO* __restrict__ x, const IO* __res
         float m[VEC], wiv[VEC], b[VEC], iv[VEC];
 #pragma unroll
         for (int v = 0; v < VEC; ++v) {
-            q[v] = (i + v) / p.inner;
-            const int c = static_cast<int>(q[v] % p.C);
+            q[v] = (WARP_RUN && v > 0) ? q[0] : run_of(i + v, p.inner);
+            const int c = channel_of_run(q[v], p.C);
             m[v] = p.mean[c];
             iv[v] = p.ivar[c];
             wiv[v] = mul_rn(p.weight[c], iv[v]);
@@ -217,19 +234,30 @@ __global__ void bn_lif_bwd_sums_kernel(const IO* __restrict__ x, const IO* __res
 #pragma unroll
         for (int t = 0; t < TMAX; ++t)
             if (t < T) gin[t] = ld_stream<IO, VEC>(g + static_cast<long long>(t) * N + i);
-        float gu[TMAX][VEC];
-        bn_lif_grad_current<IO, VEC, TMAX, FIRE>(xin, gin, T, m, wiv, b, alpha, thresh, beta, interval, gu);
+        bn_lif_grad_current<IO, VEC, TMAX, FIRE>(
+            xin, gin, T, m, wiv, b, alpha, thresh, beta, interval, [&](int t, int v, float gu) {
+                const float xhat = mul_rn(sub_rn(Elem<IO>::load(xin[t].v[v]), m[v]), iv[v]);
+                s1[v] += gu;
+                s2[v] = fmaf(gu, xhat, s2[v]);
+            });
+    }
+
+    if (WARP_RUN) {
+        float a = 0.f, c2 = 0.f;
 #pragma unroll
-        for (int t = 0; t < TMAX; ++t) {
-            if (t < T) {
+        for (int v = 0; v < VEC; ++v) { a += s1[v]; c2 += s2[v]; }
 #pragma unroll
-                for (int v = 0; v < VEC; ++v) {
-                    const float xhat = mul_rn(sub_rn(Elem<IO>::load(xin[t].v[v]), m[v]), iv[v]);
-                    s1[v] += gu[t][v];
-                    s2[v] = fmaf(gu[t][v], xhat, s2[v]);
-                }
-            }
+        for (int o = 16; o > 0; o >>= 1) {
+            a += __shfl_xor_sync(0xffffffffu, a, o);
+            c2 += __shfl_xor_sync(0xffffffffu, c2, o);
         }
+        // lane 0 of a warp is active whenever any lane of the warp is (N is a multiple of inner)
+        if ((threadIdx.x & 31) == 0 && active) {
+            const int c = channel_of_run(q[0], p.C);
+            atomicAdd(&sum_g[c], a);
+            atomicAdd(&sum_gx[c], c2);
+        }
+        return;
     }
 
     // warp inside one channel run: butterfly, one shared atomic per warp; otherwise per lane
@@ -261,7 +289,7 @@ __global__ void bn_lif_bwd_sums_kernel(const IO* __restrict__ x, const IO* __res
     for (int j = threadIdx.x; j < nq; j += blockDim.x) {
         const float a = sacc[j], c2 = sacc[nq + j];
         if (a != 0.f || c2 != 0.f) {
-            const int c = static_cast<int>((q0 + j) % p.C);
+            const int c = channel_of_run(q0 + j, p.C);
             atomicAdd(&sum_g[c], a);
             atomicAdd(&sum_gx[c], c2);
         }
@@ -272,7 +300,7 @@ __global__ void bn_lif_bwd_sums_kernel(const IO* __restrict__ x, const IO* __res
 // Backward pass 2: grad_x = gu*w*ivar - ivar*(xhat*gxhatx[c] + gxhat[c]).
 // ---------------------------------------------------------------------------------------
 template <typename IO, int VEC, int TMAX, bool FIRE>
-__global__ void bn_lif_bwd_input_kernel(const IO* __restrict__ x, const IO* __restrict__ g,
+__global__ void __launch_bounds__(256, (VEC * TMAX <= 16) ? 4 : 1) bn_lif_bwd_input_kernel(const IO* __restrict__ x, const IO* __restrict__ g,
                                         const float* __restrict__ gxhat,
                                         const float* __restrict__ gxhatx, IO* __restrict__ gx,
                                         BnParams p, int T, long long N, float alpha, float thresh,
@@ -281,16 +309,21 @@ __global__ void bn_lif_bwd_input_kernel(const IO* __restrict__ x, const IO* __re
     const long long i = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) * VEC;
     if (i >= N) return;
     float m[VEC], wiv[VEC], b[VEC], iv[VEC], wt[VEC], gh[VEC], ghx[VEC];
+    const bool one_channel = (p.inner % VEC) == 0;        // i is a multiple of VEC
 #pragma unroll
     for (int v = 0; v < VEC; ++v) {
-        const int c = channel_of(i + v, p.inner, p.C);
-        m[v] = p.mean[c];
-        iv[v] = p.ivar[c];
-        wt[v] = p.weight[c];
-        wiv[v] = mul_rn(wt[v], iv[v]);
-        b[v] = FIRE ? p.bias[c] : 0.f;
-        gh[v] = gxhat[c];
-        ghx[v] = gxhatx[c];
+        const int c = (one_channel && v > 0) ? 0 : channel_of(i + v, p.inner, p.C);
+        if (one_channel && v > 0) {
+            m[v] = m[0]; iv[v] = iv[0]; wt[v] = wt[0]; wiv[v] = wiv[0]; b[v] = b[0]; gh[v] = gh[0]; ghx[v] = ghx[0];
+        } else {
+            m[v] = p.mean[c];
+            iv[v] = p.ivar[c];
+            wt[v] = p.weight[c];
+            wiv[v] = mul_rn(wt[v], iv[v]);
+            b[v] = FIRE ? p.bias[c] : 0.f;
+            gh[v] = gxhat[c];
+            ghx[v] = gxhatx[c];
+        }
     }
     Pack<IO, VEC> xin[TMAX], gin[TMAX];
 #pragma unroll
@@ -299,22 +332,15 @@ __global__ void bn_lif_bwd_input_kernel(const IO* __restrict__ x, const IO* __re
 #pragma unroll
     for (int t = 0; t < TMAX; ++t)
         if (t < T) gin[t] = ld_stream<IO, VEC>(g + static_cast<long long>(t) * N + i);
-    float gu[TMAX][VEC];
-    bn_lif_grad_current<IO, VEC, TMAX, FIRE>(xin, gin, T, m, wiv, b, alpha, thresh, beta, interval, gu);
-#pragma unroll
-    for (int t = 0; t < TMAX; ++t) {
-        if (t < T) {
-            Pack<IO, VEC> o;
-#pragma unroll
-            for (int v = 0; v < VEC; ++v) {
-                const float xhat = mul_rn(sub_rn(Elem<IO>::load(xin[t].v[v]), m[v]), iv[v]);
-                const float lhs = mul_rn(mul_rn(gu[t][v], wt[v]), iv[v]);
-                const float rhs = mul_rn(iv[v], add_rn(mul_rn(xhat, ghx[v]), gh[v]));
-                o.v[v] = Elem<IO>::store(sub_rn(lhs, rhs));
-            }
-            st_stream<IO, VEC>(gx + static_cast<long long>(t) * N + i, o);
-        }
-    }
+    Pack<IO, VEC> o;
+    bn_lif_grad_current<IO, VEC, TMAX, FIRE>(
+        xin, gin, T, m, wiv, b, alpha, thresh, beta, interval, [&](int t, int v, float gu) {
+            const float xhat = mul_rn(sub_rn(Elem<IO>::load(xin[t].v[v]), m[v]), iv[v]);
+            const float lhs = mul_rn(mul_rn(gu, wt[v]), iv[v]);
+            const float rhs = mul_rn(iv[v], add_rn(mul_rn(xhat, ghx[v]), gh[v]));
+            o.v[v] = Elem<IO>::store(sub_rn(lhs, rhs));
+            if (v == VEC - 1) st_stream<IO, VEC>(gx + static_cast<long long>(t) * N + i, o);   // row t complete
+        });
 }
 
 // gxhat[c] = weight[c]*sum_g[c]/count ; gxhatx[c] = weight[c]*sum_gx[c]/count  (C threads)

@@ -61,6 +61,12 @@ __device__ __forceinline__ double mul_rn(double a, double b) { return __dmul_rn(
 __device__ __forceinline__ double add_rn(double a, double b) { return __dadd_rn(a, b); }
 __device__ __forceinline__ double sub_rn(double a, double b) { return __dsub_rn(a, b); }
 
+// Rectangular surrogate window of the reference, (u - th < iv) && (th - u < iv)
+// (snn_kernel_bp.cu:126). IEEE subtraction is antisymmetric, th - u == -(u - th) bit for bit,
+// so the pair of tests is exactly |u - th| < iv: one subtract and one compare.
+__device__ __forceinline__ bool inside_window(float u, float th, float iv) { return fabsf(sub_rn(u, th)) < iv; }
+__device__ __forceinline__ bool inside_window(double u, double th, double iv) { return fabs(sub_rn(u, th)) < iv; }
+
 // ---------------------------------------------------------------------------------------
 // VEC-wide packs moved with one instruction
 // ---------------------------------------------------------------------------------------
@@ -261,7 +267,7 @@ __global__ void lif_bwd_kernel(const IO* __restrict__ x, const IO* __restrict__ 
             for (int v = 0; v < VEC; ++v) {
                 const CT ut = u[t][v];
                 const CT ga = mul_rn(gu[v], alpha);
-                const bool inside = (sub_rn(ut, thresh) < interval) && (sub_rn(thresh, ut) < interval);
+                const bool inside = inside_window(ut, thresh, interval);
                 CT gs = CT(0);
                 if (inside) gs = sub_rn(Elem<IO>::load(gin[t].v[v]), mul_rn(ga, ut));
                 const CT keep = (ut <= thresh) ? CT(1) : CT(0);
@@ -315,8 +321,7 @@ __global__ void lif_bwd_mem_kernel(const typename Elem<IO>::CT* __restrict__ mem
                 for (int v = 0; v < VEC; ++v) {
                     const CT ut = uin[k].v[v];
                     const CT ga = mul_rn(gu[v], alpha);
-                    const bool inside =
-                        (sub_rn(ut, thresh) < interval) && (sub_rn(thresh, ut) < interval);
+                    const bool inside = inside_window(ut, thresh, interval);
                     CT gs = CT(0);
                     if (inside) gs = sub_rn(Elem<IO>::load(gin[k].v[v]), mul_rn(ga, ut));
                     const CT keep = (ut <= thresh) ? CT(1) : CT(0);

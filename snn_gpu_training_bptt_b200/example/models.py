@@ -39,29 +39,32 @@ class SpikingVGG(nn.Module):
     fc 8192->1024 - LIF - fc 1024->classes on the time-averaged spikes."""
 
     def __init__(self, time_steps=8, num_classes=10, act_dtype=torch.bfloat16, widths=(128, 256, 512),
-                 image=32, hidden=1024):
+                 image=32, hidden=1024, fused_pool=True):
         super().__init__()
         self.T, self.act_dtype = time_steps, act_dtype
+        self.fused_pool = fused_pool and time_steps <= 16
         w1, w2, w3 = widths
+        lif_pool = sop.FirePool if self.fused_pool else sop.Fire
         self.conv1_1 = sop.Conv(3, w1)
         self.conv1_2 = sop.FireConv(w1, w1)        # LIF of conv1_1's current, then conv
-        self.fire1 = sop.Fire()
+        self.fire1 = lif_pool()
         self.conv2_1 = sop.Conv(w1, w2)
         self.conv2_2 = sop.FireConv(w2, w2)
-        self.fire2 = sop.Fire()
+        self.fire2 = lif_pool()
         self.conv3_1 = sop.Conv(w2, w3)
         self.conv3_2 = sop.FireConv(w3, w3)
-        self.fire3 = sop.Fire()
+        self.fire3 = lif_pool()
         feat = w3 * (image // 8) ** 2
         self.fc1 = sop.Fc(feat, hidden)
         self.fire_fc = sop.Fire()
         self.fc2 = nn.Linear(hidden, num_classes)
 
     def forward(self, images):
+        pool = (lambda t: t) if self.fused_pool else _pool      # FirePool already pooled
         x = _encode(images, self.T, self.act_dtype)
-        x = _pool(self.fire1(self.conv1_2(self.conv1_1(x))))
-        x = _pool(self.fire2(self.conv2_2(self.conv2_1(x))))
-        x = _pool(self.fire3(self.conv3_2(self.conv3_1(x))))
+        x = pool(self.fire1(self.conv1_2(self.conv1_1(x))))
+        x = pool(self.fire2(self.conv2_2(self.conv2_1(x))))
+        x = pool(self.fire3(self.conv3_2(self.conv3_1(x))))
         x = x.reshape(x.shape[0], x.shape[1], -1)          # [T, B, C*H*W] in (C, H, W) order
         x = self.fire_fc(self.fc1(x))
         return self.fc2(x.mean(dim=0).float())

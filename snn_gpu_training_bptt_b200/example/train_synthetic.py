@@ -61,8 +61,14 @@ def load_checkpoint(path, model, optimizer=None):
 
 
 def run(model_name="vgg", time_steps=8, batch=64, steps=20, warmup=5, precision="bf16", lr=1e-2,
-        bucket_mb=25.0, overlap=True, seed=0, log=False, checkpoint=None):
-    """Trains for warmup+steps steps; returns a dict with samples/sec (whole job) and timings."""
+        bucket_mb=25.0, overlap=True, seed=0, log=False, checkpoint=None, graph=True,
+        return_params=False, model_kwargs=None):
+    """Trains for warmup+steps steps; returns a dict with samples/sec (whole job) and timings.
+
+    ``graph=True`` captures one whole training step (zero_grad, forward, loss, backward with its
+    bucketed all-reduces on the side stream, SGD update) into a CUDA graph after the warm-up steps
+    and replays it: a step is ~150 small launches, and at a few ms per step the Python/launch
+    overhead of issuing them one by one is as large as the GPU time itself."""
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
@@ -76,16 +82,24 @@ def run(model_name="vgg", time_steps=8, batch=64, steps=20, warmup=5, precision=
     act_dtype = {"bf16": torch.bfloat16, "fp16": torch.float16, "fp32": torch.float32}[precision]
     torch.backends.cudnn.benchmark = True
     torch.manual_seed(seed)
-    net = models.build(model_name, time_steps=time_steps, act_dtype=act_dtype).to(dev)
+    net = models.build(model_name, time_steps=time_steps, act_dtype=act_dtype, **(model_kwargs or {})).to(dev)
     model = DistributedDataParallel(net, bucket_mb=bucket_mb, overlap=overlap)
     opt = torch.optim.SGD(net.parameters(), lr=lr, momentum=0.9)
     data = SyntheticImages(batch, seed=1000 + rank)
     n_params = sum(p.numel() for p in net.parameters())
 
-    def one_step(k):
-        images, labels = data.batch(k, dev)
+    static_images = torch.empty((batch, 3, 32, 32), device=dev)
+    static_labels = torch.empty((batch,), dtype=torch.long, device=dev)
+
+    def load(k):
+        """This step's batch: pinned host memory -> the fixed device buffers the step reads."""
+        j = k % len(data.images)
+        static_images.copy_(data.images[j], non_blocking=True)
+        static_labels.copy_(data.labels[j], non_blocking=True)
+
+    def compute():
         model.zero_grad()
-        loss = F.cross_entropy(model(images), labels)
+        loss = F.cross_entropy(model(static_images), static_labels)
         loss.backward()
         opt.step()
         return loss
@@ -95,8 +109,32 @@ def run(model_name="vgg", time_steps=8, batch=64, steps=20, warmup=5, precision=
             dist.barrier()
         torch.cuda.synchronize(dev)
 
-    for k in range(warmup):
-        loss = one_step(k)
+    captured = None
+    if graph:
+        # warm up on a side stream (cuDNN autotuning, lazy optimizer state), then capture
+        side = torch.cuda.Stream(dev)
+        side.wait_stream(torch.cuda.current_stream(dev))
+        with torch.cuda.stream(side):
+            for k in range(max(warmup, 3)):
+                load(k)
+                loss = compute()
+        torch.cuda.current_stream(dev).wait_stream(side)
+        barrier()
+        captured = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(captured, capture_error_mode="thread_local"):
+            static_loss = compute()
+
+        def one_step(k):
+            load(k)
+            captured.replay()
+            return static_loss
+    else:
+        def one_step(k):
+            load(k)
+            return compute()
+
+        for k in range(warmup):
+            loss = one_step(k)
     barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     t0 = time.perf_counter()
@@ -122,8 +160,10 @@ def run(model_name="vgg", time_steps=8, batch=64, steps=20, warmup=5, precision=
         "ms_per_step": dev_ms / steps, "samples_per_s": batch * world * steps / (dev_ms / 1e3),
         "samples_per_s_wall": batch * world * steps / wall, "final_loss": final_loss,
         "h2d_bytes_per_step": data.bytes_per_batch, "d2h_bytes_per_step": 4,
-        "grad_buckets": len(model.buckets), "overlap": overlap,
+        "grad_buckets": len(model.buckets), "overlap": overlap, "cuda_graph": bool(graph),
     }
+    if return_params:
+        out["params"] = [p.detach().float().cpu() for p in net.parameters()]
     if own_group:
         dist.destroy_process_group()
     return out
@@ -139,13 +179,14 @@ def main():
     ap.add_argument("--precision", default="bf16", choices=["bf16", "fp16", "fp32"])
     ap.add_argument("--bucket-mb", type=float, default=25.0)
     ap.add_argument("--no-overlap", action="store_true")
+    ap.add_argument("--no-graph", action="store_true", help="issue every launch from Python instead of replaying a CUDA graph")
     ap.add_argument("--checkpoint", default=None)
     ap.add_argument("--log", action="store_true")
     a = ap.parse_args()
     T = a.time_steps or (8 if a.model == "vgg" else 16)
     B = a.batch or (64 if a.model == "vgg" else 128)
     res = run(a.model, T, B, a.steps, a.warmup, a.precision, bucket_mb=a.bucket_mb,
-              overlap=not a.no_overlap, log=a.log, checkpoint=a.checkpoint)
+              overlap=not a.no_overlap, log=a.log, checkpoint=a.checkpoint, graph=not a.no_graph)
     if int(os.environ.get("RANK", "0")) == 0:
         print(json.dumps(res))
 

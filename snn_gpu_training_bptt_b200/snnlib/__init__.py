@@ -61,6 +61,24 @@ def _cast(param, like):
     return param if param is None or param.dtype == like.dtype else param.to(like.dtype)
 
 
+def _add_bias(y, bias):
+    """y[:, c] += bias[c] in place with the library's channel kernel (fp32 bias, any activation
+    dtype); torch's own add for the combinations that kernel does not cover."""
+    if bias is None:
+        return y
+    if y.is_cuda and bias.dtype == torch.float32 and y.dtype in (torch.float32, torch.bfloat16, torch.float16) \
+            and _capi._channel_geometry(y) is not None:
+        return _capi.channel_bias_add_(y, bias)
+    return y.add_(bias.to(y.dtype).view((1, -1) + (1,) * (y.dim() - 2)))
+
+
+def _bias_grad(g, dtype):
+    """Sum of g ([N, C, ...]) over everything but channels, in the bias's dtype."""
+    if g.is_cuda and g.dtype in (torch.float32, torch.bfloat16, torch.float16):
+        return _capi.channel_sum(g).to(dtype)
+    return torch.sum(g, dim=[d for d in range(g.dim()) if d != 1], dtype=dtype)
+
+
 def _rows(t):
     """[T, B, ...] -> [T*B, features] view (reference flattens C,H,W: snn_kernel_fp.cu:349)."""
     return t.reshape(t.shape[0] * t.shape[1], -1)
@@ -69,16 +87,15 @@ def _rows(t):
 def fc_fp(spatial, weight_fc, bias_fc):
     """fc[t] = spatial[t] @ W^T + b for every t. Reference: snn.cpp:130-136 -> snn_kernel_fp.cu:332-357."""
     T, B = spatial.shape[0], spatial.shape[1]
-    return F.linear(_rows(spatial), _cast(weight_fc, spatial), _cast(bias_fc, spatial)).view(
-        T, B, weight_fc.shape[0])
+    y = F.linear(_rows(spatial), _cast(weight_fc, spatial))
+    return _add_bias(y, bias_fc).view(T, B, weight_fc.shape[0])
 
 
 def _fc_grads(inp_rows, grad_fc, weight_fc, dim_fc):
     g = _rows(grad_fc)
     grad_in = g @ _cast(weight_fc, g)            # [T*B, in]
     grad_w = (g.t() @ inp_rows).to(weight_fc.dtype)   # [out, in], summed over t and b
-    grad_b = torch.sum(grad_fc, dim=tuple(dim_fc), dtype=weight_fc.dtype)
-    return grad_in, grad_w, grad_b
+    return grad_in, grad_w, _bias_grad(g, weight_fc.dtype)
 
 
 def fc_bp(spatial, grad_fc, weight_fc, bias_fc, dim_fc):
@@ -116,9 +133,9 @@ def conv_fp(spatial, weight_conv, bias_conv, stride, padding, dilation, groups, 
             deterministic):
     """conv[t] = conv2d(spatial[t]). Reference: snn.cpp:239-253 -> snn_kernel_fp.cu:457-479."""
     T, B = spatial.shape[0], spatial.shape[1]
-    y = F.conv2d(_images(spatial), _cast(weight_conv, spatial), _cast(bias_conv, spatial),
-                 tuple(stride), tuple(padding), tuple(dilation), groups)
-    return y.view((T, B) + tuple(y.shape[1:]))
+    y = F.conv2d(_images(spatial), _cast(weight_conv, spatial), None, tuple(stride), tuple(padding),
+                 tuple(dilation), groups)
+    return _add_bias(y, bias_conv).view((T, B) + tuple(y.shape[1:]))
 
 
 def _conv_grads(inp, grad_conv, weight_conv, stride, padding, dilation, groups, dim_conv):
@@ -127,8 +144,7 @@ def _conv_grads(inp, grad_conv, weight_conv, stride, padding, dilation, groups, 
     grad_in, grad_w = torch.ops.aten.convolution_backward(
         g, x, _cast(weight_conv, g), None, list(stride), list(padding), list(dilation), False,
         [0, 0], groups, [True, True, False])[:2]
-    grad_b = torch.sum(grad_conv, dim=tuple(dim_conv), dtype=weight_conv.dtype)
-    return grad_in, grad_w.to(weight_conv.dtype), grad_b
+    return grad_in, grad_w.to(weight_conv.dtype), _bias_grad(g, weight_conv.dtype)
 
 
 def conv_bp(spatial, grad_conv, weight_conv, stride, padding, dilation, groups, benchmark,

@@ -12,7 +12,7 @@ lines 25-28): membrane potentials are never stored, the backward kernel rebuilds
 """
 import torch
 
-from . import snnlib
+from . import _capi, snnlib
 from ._capi import as_time_major_dense
 
 # hyper-parameters (reference snnlib_func.py:11-17)
@@ -49,6 +49,25 @@ class FireFunc(torch.autograd.Function):
 
 
 fire_func = FireFunc.apply
+
+
+class FirePoolFunc(torch.autograd.Function):
+    """LIF followed by AvgPool2d(2) on every time step, as one kernel each way (an addition to the
+    reference's set of Functions; equals ``avg_pool2d(fire_func(x))`` applied per time step)."""
+
+    @staticmethod
+    def forward(ctx, spatial):
+        dense, pooled = _capi.lif_pool_fwd(spatial, alpha, thresh)
+        ctx.save_for_backward(dense)
+        return pooled
+
+    @staticmethod
+    def backward(ctx, grad_pooled):
+        (dense,) = ctx.saved_tensors
+        return _capi.lif_pool_bwd(dense, grad_pooled, alpha, thresh, beta, interval)
+
+
+fire_pool_func = FirePoolFunc.apply
 
 
 class BnFunc(torch.autograd.Function):

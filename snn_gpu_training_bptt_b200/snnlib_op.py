@@ -27,6 +27,14 @@ class Fire(nn.Module):
         return sf.fire_func(x)
 
 
+class FirePool(nn.Module):
+    """LIF layer followed by AvgPool2d(2) per time step, fused (not in the reference's layer set;
+    numerically identical to ``Fire`` then pooling each x[t])."""
+
+    def forward(self, x):
+        return sf.fire_pool_func(x)
+
+
 # ------------------------------------------------------------------------------------------
 # shared batch-norm bookkeeping
 # ------------------------------------------------------------------------------------------

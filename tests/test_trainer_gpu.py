@@ -179,3 +179,81 @@ def test_reference_cifar_bn_network_trains_and_evaluates():
         assert out.shape == (4, 10) and torch.isfinite(out).all()
     finally:
         sf.time_step = old_T
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("shape", [(8, 2, 16, 8, 8), (6, 3, 5, 4, 6), (16, 1, 8, 4, 4), (4, 2, 130, 2, 2), (1, 1, 4, 2, 2)])
+def test_fused_lif_pool_equals_lif_then_pool(dtype, shape):
+    """FirePool == Fire followed by AvgPool2d(2) on every time step, forward and backward, bit for
+    bit (pooled spikes are k/4, the pooled gradient is scaled by an exact 1/4); and in fp32 also
+    equal to the CPU oracle's LIF composed with numpy pooling."""
+    from snn_gpu_training_bptt_b200 import snnlib_func as sf
+    T, B, C, H, W = shape
+    gen = torch.Generator().manual_seed(sum(shape))
+    x = (0.5 + torch.randn(shape, generator=gen)).to(dtype)
+    g = torch.randn((T, B, C, H // 2, W // 2), generator=gen).to(dtype)
+    a = x.cuda().requires_grad_(True)
+    b = x.cuda().requires_grad_(True)
+    ya = F.avg_pool2d(sf.fire_func(a).reshape(T * B, C, H, W), 2).view(T, B, C, H // 2, W // 2)
+    yb = sf.fire_pool_func(b)
+    assert yb.shape == ya.shape and torch.equal(ya, yb)
+    ya.backward(g.cuda())
+    yb.backward(g.cuda())
+    assert torch.equal(a.grad, b.grad)
+    if dtype == torch.float32:
+        s_ref, _ = orc.c_lif_fwd(x.numpy())
+        pooled = s_ref.reshape(T, B, C, H // 2, 2, W // 2, 2).mean(axis=(4, 6))
+        assert np.array_equal(yb.detach().cpu().numpy(), pooled)
+        g_full = np.repeat(np.repeat(g.numpy(), 2, axis=3), 2, axis=4) * np.float32(0.25)
+        assert np.array_equal(b.grad.cpu().numpy(), orc.c_lif_bwd(x.numpy(), np.ascontiguousarray(g_full)))
+
+
+def test_fused_and_unfused_pool_networks_agree():
+    from snn_gpu_training_bptt_b200.example import models
+    images = torch.rand(2, 3, 16, 16, device="cuda")
+    labels = torch.tensor([3, 5], device="cuda")
+    grads = []
+    for fused in (True, False):
+        torch.manual_seed(4)
+        net = models.SpikingVGG(time_steps=4, widths=(8, 16, 16), hidden=32, image=16,
+                                act_dtype=torch.float32, fused_pool=fused).cuda()
+        loss = F.cross_entropy(net(images), labels)
+        loss.backward()
+        grads.append((float(loss.detach()), {n: p.grad.clone() for n, p in net.named_parameters()}))
+    assert abs(grads[0][0] - grads[1][0]) < 1e-6
+    for n in grads[0][1]:
+        assert_grad_close(grads[0][1][n].cpu(), grads[1][1][n].cpu(), rtol=1e-3, atol=1e-6, what=n)
+
+
+def test_cuda_graph_training_matches_eager():
+    """The captured training step replays to the same parameters as the eager loop."""
+    from snn_gpu_training_bptt_b200.example import train_synthetic
+    outs = [train_synthetic.run("vgg", time_steps=4, batch=4, steps=4, warmup=3, precision="bf16",
+                                graph=flag, return_params=True, model_kwargs=dict(widths=(16, 32, 32), hidden=64))
+            for flag in (False, True)]
+    assert np.isfinite(outs[1]["final_loss"])
+    assert abs(outs[0]["final_loss"] - outs[1]["final_loss"]) < 5e-2
+    for a, b in zip(outs[0]["params"], outs[1]["params"]):
+        assert torch.allclose(a, b, rtol=5e-2, atol=5e-3)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_channel_bias_add_and_sum_kernels(dtype):
+    """snn_channel_bias_add / snn_channel_sum against torch on contiguous, channels-last and
+    matrix layouts, narrow and very wide channel counts, ragged sizes."""
+    from snn_gpu_training_bptt_b200 import _capi
+    gen = torch.Generator().manual_seed(0)
+    cases = [((512, 128, 8, 8), True), ((512, 128, 8, 8), False), ((37, 5, 3, 7), False), ((37, 6, 3, 7), True),
+             ((2048, 1024), False), ((33, 9000), False), ((3, 7), False), ((64, 96, 4, 4), True)]
+    for shape, channels_last in cases:
+        y = torch.randn(shape, generator=gen).to(dtype).cuda()
+        if channels_last:
+            y = y.contiguous(memory_format=torch.channels_last)
+        bias = torch.randn(shape[1], generator=gen).cuda()
+        want = (y.float() + bias.view((1, -1) + (1,) * (len(shape) - 2))).to(dtype)
+        got = _capi.channel_bias_add_(y.clone(memory_format=torch.preserve_format), bias)
+        assert got.stride() == y.stride() and torch.equal(got, want), shape
+        sums = _capi.channel_sum(y)
+        ref = y.double().sum(dim=[d for d in range(len(shape)) if d != 1])
+        scale = float(y.float().abs().sum(dim=[d for d in range(len(shape)) if d != 1]).max())
+        assert float((sums.double() - ref).abs().max()) <= 2e-6 * scale + 1e-6, shape
