@@ -196,6 +196,26 @@ int snn_channel_bias_add(void *y, const float *bias, int64_t outer, int64_t C, i
 int snn_channel_sum(const void *grad, float *out, int64_t outer, int64_t C, int64_t inner,
                     int dtype, void *stream);
 
+/* ----------------------------------------------------------------------------------------
+ * Fused synaptic linear + LIF forward on the tcgen05 tensor cores (bf16 operands, fp32
+ * accumulation in tensor memory, LIF recurrence in the GEMM epilogue):
+ *   current[t, b, :] = bf16( x[t, b, :] @ weight^T + bias ) ;  spike = LIF over t of current
+ * Replaces `Fc` followed by `Fire` of the reference: fc_fp (snnlib/cuda/snn.cpp:130-136 ->
+ * snn_kernel_fp.cu:332-357, T cuBLAS calls) then fire_s_fp (snn.cpp:11-17).
+ *   x [T, B, K] bf16, weight [M, K] bf16 (both 16-byte aligned), bias [M] fp32 or NULL,
+ *   current [T, B, M] bf16 or NULL (the LIF input; backward re-reads it), spike [T, B, M] bf16.
+ * Supported when snn_linear_lif_fwd_supported() returns 1: SNN_BF16, T in {4, 8},
+ * B % (128/T) == 0, K % 64 == 0, M % 128 == 0; otherwise SNN_ERR_UNSUPPORTED (use snn_lif_fwd
+ * after a library GEMM). Waits inside the kernel are bounded; snn_linear_lif_error() returns 0,
+ * or the code of the wait that expired (1 producer, 2 MMA issuer, 3 epilogue) after synchronising
+ * with the device, and clears it when `reset` is non-zero.
+ * -------------------------------------------------------------------------------------- */
+int snn_linear_lif_fwd_supported(int64_t T, int64_t B, int64_t K, int64_t M, int dtype);
+int snn_linear_lif_fwd(const void *x, const void *weight, const float *bias, void *current,
+                       void *spike, int64_t T, int64_t B, int64_t K, int64_t M, int dtype,
+                       float alpha, float thresh, void *stream);
+int snn_linear_lif_error(int reset);
+
 /*
  * LIF backward through time for callers that may not allocate device memory.
  *

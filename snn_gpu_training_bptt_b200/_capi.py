@@ -30,6 +30,9 @@ SIGNATURES = {
     "snn_lif_bwd_noalloc": (_int, [_vp, _vp, _vp, _i64, _i64, _int, _f32, _f32, _f32, _f32, _vp]),
     "snn_lif_pool_fwd": (_int, [_vp, _vp, _i64, _i64, _i64, _i64, _i64, _int, _f32, _f32, _vp]),
     "snn_lif_pool_bwd": (_int, [_vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _int, _f32, _f32, _f32, _f32, _vp]),
+    "snn_linear_lif_fwd_supported": (_int, [_i64, _i64, _i64, _i64, _int]),
+    "snn_linear_lif_fwd": (_int, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _int, _f32, _f32, _vp]),
+    "snn_linear_lif_error": (_int, [_int]),
     "snn_channel_bias_add": (_int, [_vp, _vp, _i64, _i64, _i64, _int, _vp]),
     "snn_channel_sum": (_int, [_vp, _vp, _i64, _i64, _i64, _int, _vp]),
     "snn_bn_lif_fwd": (_int, [_vp, _vp, _vp, _vp, _vp, _f32, _vp, _vp, _vp, _i64, _i64, _i64, _i64,
@@ -407,3 +410,39 @@ def channel_sum(grad):
                                    _stream(grad.device))
     check("snn_channel_sum", rc)
     return out
+
+
+# ----------------------------------------------------------------------------------------------
+# fused synaptic linear + LIF forward (tcgen05)
+# ----------------------------------------------------------------------------------------------
+def linear_lif_supported(x, weight):
+    """True if the tcgen05 kernel covers this problem (bf16, T in {4, 8}, tile-aligned sizes)."""
+    if x.dim() != 3 or weight.dim() != 2 or x.dtype != torch.bfloat16 or not x.is_cuda:
+        return False
+    T, B, K = x.shape
+    return bool(lib().snn_linear_lif_fwd_supported(T, B, K, weight.shape[0], DTYPE_CODE[x.dtype]))
+
+
+def linear_lif_fwd(x, weight, bias, alpha, thresh, want_current=True):
+    """(current, spike) of ``LIF(x @ weight^T + bias)`` in one kernel. x [T, B, K] bf16, weight
+    [M, K] (cast to bf16 if needed), bias fp32 [M] or None."""
+    if not linear_lif_supported(x, weight):
+        raise ValueError("linear_lif_fwd: unsupported problem (needs bf16, T in {4, 8}, B % (128/T) == 0, "
+                         "K % 64 == 0, M % 128 == 0)")
+    x = x.contiguous()
+    w = weight.to(torch.bfloat16).contiguous()
+    b = bias.float().contiguous() if bias is not None else None
+    T, B, K = x.shape
+    M = w.shape[0]
+    with torch.cuda.device(x.device):
+        spike = torch.empty((T, B, M), dtype=torch.bfloat16, device=x.device)
+        current = torch.empty_like(spike) if want_current else None
+        rc = lib().snn_linear_lif_fwd(_ptr(x), _ptr(w), _ptr(b), _ptr(current), _ptr(spike), T, B, K, M,
+                                      DTYPE_CODE[x.dtype], float(alpha), float(thresh), _stream(x.device))
+    check("snn_linear_lif_fwd", rc)
+    return current, spike
+
+
+def linear_lif_error(reset=True):
+    """0, or the code of a bounded wait that expired inside the fused kernel (synchronises)."""
+    return lib().snn_linear_lif_error(1 if reset else 0)

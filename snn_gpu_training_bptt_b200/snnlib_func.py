@@ -169,6 +169,33 @@ class FcFunc(torch.autograd.Function):
 fc_func = FcFunc.apply
 
 
+class FcFireFunc(torch.autograd.Function):
+    """Synaptic linear followed by LIF: ``fire_func(fc_func(x, W, b))`` as one op (an addition to
+    the reference's set of Functions). For bf16 problems the tcgen05 kernel covers, forward is a
+    single fused GEMM + LIF-epilogue launch; otherwise one library GEMM and the LIF kernel. The
+    LIF input current is saved (bf16 / input dtype) for the backward pass: LIF reverse pass, then
+    the two gradient GEMMs."""
+
+    @staticmethod
+    def forward(ctx, spatial, weight_fc, bias_fc):
+        if spatial.dim() == 3 and _capi.linear_lif_supported(spatial, weight_fc):
+            current, spike = _capi.linear_lif_fwd(spatial, weight_fc, bias_fc, alpha, thresh)
+        else:
+            current = snnlib.fc_fp(spatial, weight_fc, bias_fc)
+            spike = snnlib.fire_s_fp(current, alpha, thresh)
+        ctx.save_for_backward(spatial, weight_fc, bias_fc, current)
+        return spike
+
+    @staticmethod
+    def backward(ctx, grad_spike):
+        spatial, weight_fc, bias_fc, current = ctx.saved_tensors
+        grad_current = snnlib.fire_bp(current, grad_spike, alpha, thresh, beta, interval)
+        return tuple(snnlib.fc_bp(spatial, grad_current, weight_fc, bias_fc, _DIM_FC))
+
+
+fc_fire_func = FcFireFunc.apply
+
+
 def _conv_grad_tuple(grads, head, if_bias_conv, tail):
     """(input/bn grads..., Nones, grad_w, grad_b or None, Nones): layout of reference lines 183-191."""
     gw, gb = grads[-2], grads[-1]

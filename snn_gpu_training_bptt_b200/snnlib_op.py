@@ -35,6 +35,19 @@ class FirePool(nn.Module):
         return sf.fire_pool_func(x)
 
 
+class FcFire(nn.Module):
+    """Synaptic linear followed by LIF as one op (``Fc`` then ``Fire`` of the reference; fused on
+    the tensor cores for bf16 inputs with tile-aligned sizes). Parameters as ``Fc``."""
+
+    def __init__(self, cin, cout):
+        super().__init__()
+        self.weight_fc = nn.Parameter(torch.zeros(cout, cin).normal_(0, 0.75 / math.sqrt(cin)))
+        self.bias_fc = nn.Parameter(torch.zeros(cout))
+
+    def forward(self, x):
+        return sf.fc_fire_func(x, self.weight_fc, self.bias_fc)
+
+
 # ------------------------------------------------------------------------------------------
 # shared batch-norm bookkeeping
 # ------------------------------------------------------------------------------------------
