@@ -378,6 +378,35 @@ def _time_kernel(fn, reps, flush=None):
     return statistics.median(times)
 
 
+def _time_graphed(fn, reps=20, per_graph=10):
+    """Device time per call of fn() in ms with the host out of the picture: `per_graph` calls are
+    captured into one CUDA graph and the graph is replayed `reps` times (median). For kernels of a
+    few tens of microseconds the Python / launch overhead of an eager call is longer than the
+    kernel, so eager event timing would measure the host."""
+    import torch
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        for _ in range(3):
+            fn()
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        for _ in range(per_graph):
+            fn()
+    times = []
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    graph.replay()
+    for _ in range(reps):
+        e0.record()
+        graph.replay()
+        e1.record()
+        e1.synchronize()
+        times.append(e0.elapsed_time(e1) / per_graph)
+    return statistics.median(times)
+
+
 def run_sweep(args):
     """Single-GPU bandwidth sweep: T in {4,8,16} x N in {2^20,2^22,2^24,2^26}, fp32 and bf16 I/O."""
     import torch
@@ -460,33 +489,54 @@ def run_bn_lif(args):
 
 
 def run_linear_lif(args):
-    """Synaptic linear followed by LIF (T=8, batch 256, 2048 -> 2048), forward + BPTT backward with
-    weight, bias and input gradients; Bernoulli(0.2) input spikes, Kaiming-uniform weights."""
+    """Synaptic linear followed by LIF (T=8, batch 256, 2048 -> 2048): Bernoulli(0.2) input spikes,
+    Kaiming-uniform weights. Forward alone (fused tcgen05 kernel vs library GEMM + LIF kernel) and
+    forward + BPTT backward with weight, bias and input gradients."""
     import torch
-    from snn_gpu_training_bptt_b200 import snnlib_func as sf
+    from snn_gpu_training_bptt_b200 import _capi, snnlib, snnlib_func as sf
     dev = torch.device("cuda", 0)
     torch.cuda.set_device(dev)
     T, B, K, M = 8, 256, 2048, 2048
     torch.manual_seed(1234)
     lin = torch.nn.Linear(K, M).to(dev)
-    flops = 2.0 * T * B * K * M * 3
-    for dtype, name in ((torch.float32, "fp32 (TF32 off)"), (torch.bfloat16, "bf16")):
-        torch.backends.cuda.matmul.allow_tf32 = False
+    fwd_flops, all_flops = 2.0 * T * B * K * M, 2.0 * T * B * K * M * 3
+    torch.backends.cuda.matmul.allow_tf32 = False
+    peak_tf = None
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            peak_tf = float(json.load(f)["bf16_tflops"])
+    except Exception:
+        peak_tf = 1590.0
+
+    def line(name, path, flops, ms, dtype):
+        tf = flops / ms / 1e9
+        print(json.dumps({"metric": name, "value": round(tf, 1), "unit": "TFLOP/s", "dtype": dtype,
+                          "ms": round(ms, 4), "frac_of_bf16_burst_peak": round(tf / peak_tf, 4),
+                          "config": {"workload": "fc 2048->2048 + LIF, T=8, batch 256", "path": path}}))
+
+    xb = (torch.rand((T, B, K), device=dev) < 0.2).to(torch.bfloat16)
+    wb = lin.weight.detach().to(torch.bfloat16)
+    bias = lin.bias.detach().float()
+    assert _capi.linear_lif_supported(xb, wb)
+    ms = _time_graphed(lambda: _capi.linear_lif_fwd(xb, wb, bias, ALPHA, THRESH))
+    line("linear_lif_fwd_tflops", "fused: tcgen05 GEMM with the LIF recurrence in its epilogue (1 launch)", fwd_flops, ms, "bf16")
+    assert _capi.linear_lif_error() == 0
+    ms = _time_graphed(lambda: snnlib.fire_s_fp(snnlib.fc_fp(xb, wb, bias), ALPHA, THRESH))
+    line("linear_lif_fwd_tflops", "unfused: cuBLAS GEMM over T*B rows + bias kernel + snn_lif_fwd", fwd_flops, ms, "bf16")
+    ms = _time_graphed(lambda: torch.nn.functional.linear(xb.view(T * B, K), wb))
+    line("linear_fwd_tflops", "cuBLAS GEMM alone (no bias, no LIF), for scale", fwd_flops, ms, "bf16")
+
+    for dtype, name in ((torch.bfloat16, "bf16"), (torch.float32, "fp32 (TF32 off)")):
         x = (torch.rand((T, B, K), device=dev) < 0.2).to(dtype).requires_grad_(True)
         w = lin.weight.detach().clone().requires_grad_(True)
-        bias = lin.bias.detach().clone().requires_grad_(True)
+        b = lin.bias.detach().clone().requires_grad_(True)
         gs = torch.randn((T, B, M), device=dev).to(dtype)
-
-        def step():
-            x.grad = w.grad = bias.grad = None
-            s = sf.fire_func(sf.fc_func(x, w, bias))
-            s.backward(gs)
-        ms = _time_kernel(step, 20)
-        print(json.dumps({
-            "metric": "linear_lif_fwd_bwd_tflops", "value": round(flops / ms / 1e9, 1), "unit": "TFLOP/s",
-            "dtype": name, "ms_per_step": round(ms, 4),
-            "config": {"workload": "fc 2048->2048 + LIF, T=8, batch 256, fwd + BPTT bwd (dX, dW, db)",
-                       "path": "one cuBLAS GEMM over the merged T*B rows + snn_lif_fwd / snn_lif_bwd"}}))
+        for label, op in (("FcFire op (fused forward where supported)", lambda: sf.fc_fire_func(x, w, b)),
+                          ("fire_func(fc_func(x)) (library GEMM + LIF kernels)", lambda: sf.fire_func(sf.fc_func(x, w, b)))):
+            def step():
+                x.grad = w.grad = b.grad = None
+                op().backward(gs)
+            line("linear_lif_fwd_bwd_tflops", label, all_flops, _time_graphed(step), name)
 
 
 def main():

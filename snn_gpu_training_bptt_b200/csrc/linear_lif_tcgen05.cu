@@ -279,6 +279,33 @@ bool make_map(CUtensorMap* map, const void* base, int rank, const cuuint64_t* di
                CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// Encoding a tensor map costs a few microseconds of host time, comparable to the kernel itself for
+// small layers, and a training loop calls with the same buffers step after step: keep the last
+// few maps keyed by everything that went into them.
+struct MapKey {
+    const void* base; int rank; cuuint64_t dims[3]; cuuint32_t box[3];
+    bool operator==(const MapKey& o) const {
+        if (base != o.base || rank != o.rank) return false;
+        for (int i = 0; i < 3; ++i) if (dims[i] != o.dims[i] || box[i] != o.box[i]) return false;
+        return true;
+    }
+};
+bool cached_map(CUtensorMap* out, const void* base, int rank, const cuuint64_t* dims, const cuuint64_t* strides,
+                const cuuint32_t* box) {
+    constexpr int kSlots = 16;
+    thread_local MapKey keys[kSlots];
+    thread_local CUtensorMap maps[kSlots];
+    thread_local int used = 0, next = 0;
+    MapKey k{base, rank, {dims[0], dims[1], rank > 2 ? dims[2] : 1}, {box[0], box[1], rank > 2 ? box[2] : 1}};
+    for (int i = 0; i < used; ++i)
+        if (keys[i] == k) { *out = maps[i]; return true; }
+    if (!make_map(out, base, rank, dims, strides, box)) return false;
+    const int slot = used < kSlots ? used++ : (next++ % kSlots);
+    keys[slot] = k;
+    maps[slot] = *out;
+    return true;
+}
+
 template <int T>
 int launch(const CUtensorMap& mw, const CUtensorMap& mx, const float* bias, void* current, void* spike, int B, int K,
            int M, float alpha, float thresh, cudaStream_t st) {
@@ -324,7 +351,7 @@ int snn_linear_lif_fwd(const void* x, const void* weight, const float* bias, voi
     const cuuint64_t xdims[3] = {static_cast<cuuint64_t>(K), static_cast<cuuint64_t>(B), static_cast<cuuint64_t>(T)};
     const cuuint64_t xstr[2] = {static_cast<cuuint64_t>(K) * 2, static_cast<cuuint64_t>(B) * K * 2};
     const cuuint32_t xbox[3] = {BK, static_cast<cuuint32_t>(BN / T), static_cast<cuuint32_t>(T)};
-    if (!make_map(&mw, weight, 2, wdims, wstr, wbox) || !make_map(&mx, x, 3, xdims, xstr, xbox)) {
+    if (!cached_map(&mw, weight, 2, wdims, wstr, wbox) || !cached_map(&mx, x, 3, xdims, xstr, xbox)) {
         snn_internal::set_last_cuda_error(static_cast<int>(cudaErrorInvalidValue));
         return SNN_ERR_CUDA;
     }
