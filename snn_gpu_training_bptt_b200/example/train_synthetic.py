@@ -164,6 +164,12 @@ def run(model_name="vgg", time_steps=8, batch=64, steps=20, warmup=5, precision=
     }
     if return_params:
         out["params"] = [p.detach().float().cpu() for p in net.parameters()]
+    # A captured step holds NCCL work that refers to the communicator: release the graph before
+    # the process group goes away (tearing the group down under a live graph blocks forever).
+    if captured is not None:
+        torch.cuda.synchronize(dev)
+        captured.reset()
+        captured = None
     if own_group:
         dist.destroy_process_group()
     return out
@@ -183,6 +189,10 @@ def main():
     ap.add_argument("--checkpoint", default=None)
     ap.add_argument("--log", action="store_true")
     a = ap.parse_args()
+    watchdog = os.environ.get("SNN_TRAIN_WATCHDOG_S")
+    if watchdog:   # dump every thread's Python stack and exit if the run is still going after N seconds
+        import faulthandler
+        faulthandler.dump_traceback_later(int(watchdog), exit=True)
     T = a.time_steps or (8 if a.model == "vgg" else 16)
     B = a.batch or (64 if a.model == "vgg" else 128)
     res = run(a.model, T, B, a.steps, a.warmup, a.precision, bucket_mb=a.bucket_mb,
