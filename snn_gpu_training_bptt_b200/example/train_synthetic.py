@@ -175,6 +175,31 @@ def run(model_name="vgg", time_steps=8, batch=64, steps=20, warmup=5, precision=
     return out
 
 
+def profile_steps(model_name, time_steps, batch, precision, steps=3):
+    """Kernel-level table (torch.profiler) of a few eager training steps on one GPU."""
+    from torch.profiler import ProfilerActivity, profile
+    act_dtype = {"bf16": torch.bfloat16, "fp16": torch.float16, "fp32": torch.float32}[precision]
+    torch.backends.cudnn.benchmark = True
+    net = models.build(model_name, time_steps=time_steps, act_dtype=act_dtype).cuda()
+    opt = torch.optim.SGD(net.parameters(), lr=1e-2, momentum=0.9)
+    images = torch.rand(batch, 3, 32, 32, device="cuda")
+    labels = torch.randint(0, 10, (batch,), device="cuda")
+
+    def step():
+        opt.zero_grad()
+        F.cross_entropy(net(images), labels).backward()
+        opt.step()
+
+    for _ in range(5):
+        step()
+    torch.cuda.synchronize()
+    with profile(activities=[ProfilerActivity.CPU, ProfilerActivity.CUDA]) as prof:
+        for _ in range(steps):
+            step()
+        torch.cuda.synchronize()
+    return prof.key_averages().table(sort_by="cuda_time_total", row_limit=40, max_name_column_width=70)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--model", default="vgg", choices=["vgg", "resnet19"])
@@ -188,6 +213,8 @@ def main():
     ap.add_argument("--no-graph", action="store_true", help="issue every launch from Python instead of replaying a CUDA graph")
     ap.add_argument("--checkpoint", default=None)
     ap.add_argument("--log", action="store_true")
+    ap.add_argument("--profile", action="store_true",
+                    help="print a torch.profiler kernel table of 3 eager single-GPU steps instead of timing")
     a = ap.parse_args()
     watchdog = os.environ.get("SNN_TRAIN_WATCHDOG_S")
     if watchdog:   # dump every thread's Python stack and exit if the run is still going after N seconds
@@ -195,6 +222,9 @@ def main():
         faulthandler.dump_traceback_later(int(watchdog), exit=True)
     T = a.time_steps or (8 if a.model == "vgg" else 16)
     B = a.batch or (64 if a.model == "vgg" else 128)
+    if a.profile:
+        print(profile_steps(a.model, T, B, a.precision))
+        return
     res = run(a.model, T, B, a.steps, a.warmup, a.precision, bucket_mb=a.bucket_mb,
               overlap=not a.no_overlap, log=a.log, checkpoint=a.checkpoint, graph=not a.no_graph)
     if int(os.environ.get("RANK", "0")) == 0:
