@@ -16,6 +16,9 @@
 // reads, for t = 0..T-1, the 128/T consecutive columns of that time step (tcgen05.ld 32x32b) and
 // carries u / gate of its 128/T batch items in registers across the T loads.
 //
+// Two kernels share the pieces below: a one-tile-per-CTA version and, the default, a persistent
+// version (further down) that overlaps the epilogue of one tile with the MMAs of the next.
+//
 // Pipeline (192 threads): warp 4 = TMA producer (one lane), warp 5 = MMA issuer (one lane, also
 // owns the TMEM allocation), warps 0-3 = epilogue (128 lanes of TMEM). STAGES shared-memory
 // stages of {W tile 128x64, X tile 128x64} bf16 with 128-byte swizzle; full/empty mbarriers per
@@ -29,6 +32,7 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <stdlib.h>
 
 namespace snn_internal {
 void set_last_cuda_error(int e);   // defined in lif_capi.cu
@@ -252,6 +256,188 @@ linear_lif_fwd_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
     }
 }
 
+// ---------------------------------------------------------------------------------------------
+// Persistent variant: one CTA per SM walks a strided list of output tiles. Two accumulators in
+// tensor memory (2 x 128 columns) let the LIF epilogue of tile i run while the MMAs of tile i+1
+// fill the other one; the epilogue writes its bf16 currents / spikes into a shared-memory tile
+// laid out [t][b][m] and hands it to one 3-D TMA store per output instead of 2-byte stores.
+// ---------------------------------------------------------------------------------------------
+constexpr int PSTAGES = 4;
+constexpr uint32_t kTmemColsPersistent = 256;
+
+struct __align__(1024) PersistentStorage {
+    __nv_bfloat16 a[PSTAGES][BM * BK];
+    __nv_bfloat16 b[PSTAGES][BN * BK];
+    __nv_bfloat16 out_spike[BN * BM];      // [n = t*BT + j][m]
+    __nv_bfloat16 out_current[BN * BM];
+    uint64_t full[PSTAGES];
+    uint64_t empty[PSTAGES];
+    uint64_t acc_full[2];
+    uint64_t acc_empty[2];
+    uint32_t tmem_base;
+    uint32_t epi_ok;
+};
+
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tma_store_3d(const CUtensorMap* map, const void* src, int c0, int c1, int c2) {
+    asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];" ::"l"(map),
+                 "r"(smem_u32(src)), "r"(c0), "r"(c1), "r"(c2)
+                 : "memory");
+}
+__device__ __forceinline__ void epilogue_barrier() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+
+template <int T>
+__global__ void __launch_bounds__(kThreads, 1)
+linear_lif_fwd_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
+                                 const __grid_constant__ CUtensorMap map_spike,
+                                 const __grid_constant__ CUtensorMap map_current, int write_current,
+                                 const float* __restrict__ bias, int B, int K, int M, float alpha, float thresh)
+{
+    constexpr int BT = BN / T;
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
+    PersistentStorage& sm = *reinterpret_cast<PersistentStorage*>(
+        (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int num_kb = K / BK;
+    const int tiles_m = M / BM;
+    const int num_tiles = tiles_m * (B / BT);
+
+    if (threadIdx.x == 4 * 32) {
+        for (int s = 0; s < PSTAGES; ++s) { mbar_init(&sm.full[s], 1); mbar_init(&sm.empty[s], 1); }
+        for (int i = 0; i < 2; ++i) { mbar_init(&sm.acc_full[i], 1); mbar_init(&sm.acc_empty[i], 128); }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_x) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_spike) : "memory");
+    }
+    if (warp == 5) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sm.tmem_base)),
+                     "r"(kTmemColsPersistent)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = sm.tmem_base;
+
+    if (warp == 4) {
+        // ------------------------------ TMA producer ------------------------------
+        if (lane == 0) {
+            int it = 0;                                   // stage counter runs on across tiles
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+                const int m0 = (tile % tiles_m) * BM, b0 = (tile / tiles_m) * BT;
+                for (int kb = 0; kb < num_kb; ++kb, ++it) {
+                    const int s = it % PSTAGES;
+                    const uint32_t parity = ((it / PSTAGES) & 1) ^ 1;
+                    if (!mbar_wait(&sm.empty[s], parity)) { atomicExch(&g_linear_lif_error, 1); ok = false; break; }
+                    mbar_expect_tx(&sm.full[s], kStageBytesA + kStageBytesB);
+                    tma_load_2d(sm.a[s], &map_w, &sm.full[s], kb * BK, m0);
+                    tma_load_3d(sm.b[s], &map_x, &sm.full[s], kb * BK, b0, 0);
+                }
+            }
+        }
+    } else if (warp == 5) {
+        // ------------------------------ MMA issuer --------------------------------
+        if (lane == 0) {
+            constexpr uint32_t idesc = umma_idesc_bf16(BM, BN);
+            int it = 0, local = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
+                const int buf = local & 1;
+                const uint32_t acc_parity = ((local >> 1) & 1) ^ 1;      // first use of a buffer passes
+                if (!mbar_wait(&sm.acc_empty[buf], acc_parity)) { atomicExch(&g_linear_lif_error, 4); break; }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t tmem_acc = tmem_base + buf * BN;
+                for (int kb = 0; kb < num_kb; ++kb, ++it) {
+                    const int s = it % PSTAGES;
+                    const uint32_t parity = (it / PSTAGES) & 1;
+                    if (!mbar_wait(&sm.full[s], parity)) { atomicExch(&g_linear_lif_error, 2); ok = false; break; }
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const uint64_t da = umma_desc_sw128(sm.a[s]);
+                    const uint64_t db = umma_desc_sw128(sm.b[s]);
+#pragma unroll
+                    for (int k = 0; k < BK / UMMA_K; ++k)
+                        umma_bf16(tmem_acc, da + 2 * k, db + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
+                    umma_commit(&sm.empty[s]);
+                }
+                if (ok) umma_commit(&sm.acc_full[buf]);
+            }
+        }
+    } else {
+        // ------------------------------ epilogue warps 0-3 ------------------------
+        const int row = warp * 32 + lane;                 // TMEM lane = output neuron inside the tile
+        int local = 0;
+        for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++local) {
+            const int m0 = (tile % tiles_m) * BM, b0 = (tile / tiles_m) * BT;
+            const int buf = local & 1;
+            const uint32_t acc_parity = (local >> 1) & 1;
+            if (threadIdx.x == 0) {
+                const bool ok0 = mbar_wait(&sm.acc_full[buf], acc_parity);
+                if (!ok0) atomicExch(&g_linear_lif_error, 3);
+                // the previous tile's TMA stores must have finished reading the staging tiles
+                asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+                sm.epi_ok = ok0 ? 1u : 0u;
+            }
+            epilogue_barrier();
+            if (sm.epi_ok == 0u) break;
+            mbar_wait(&sm.acc_full[buf], acc_parity);     // already complete: returns at once, orders this thread
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+
+            const float bias_m = bias != nullptr ? bias[m0 + row] : 0.f;
+            float u[BT], gate[BT];
+#pragma unroll
+            for (int j = 0; j < BT; ++j) { u[j] = 0.f; gate[j] = 1.f; }
+            const uint32_t lane_base = tmem_base + buf * BN + (static_cast<uint32_t>(warp * 32) << 16);
+#pragma unroll
+            for (int t = 0; t < T; ++t) {
+#pragma unroll
+                for (int c = 0; c < BT; c += 16) {
+                    uint32_t r[16];
+                    tmem_ld16(lane_base + t * BT + c, r);
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        const __nv_bfloat16 cur_h = __float2bfloat16_rn(__fadd_rn(__uint_as_float(r[j]), bias_m));
+                        const float cur = __bfloat162float(cur_h);
+                        const float leak = __fmul_rn(__fmul_rn(alpha, u[c + j]), gate[c + j]);
+                        u[c + j] = __fadd_rn(leak, cur);
+                        const bool s = u[c + j] > thresh;
+                        gate[c + j] = s ? 0.f : 1.f;
+                        const int n = t * BT + c + j;
+                        sm.out_spike[n * BM + row] = __float2bfloat16_rn(s ? 1.f : 0.f);
+                        sm.out_current[n * BM + row] = cur_h;
+                    }
+                }
+            }
+            // accumulator drained: hand the TMEM buffer back to the MMA warp
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            mbar_arrive(&sm.acc_empty[buf]);
+            // staging tiles complete: one thread issues the bulk stores
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            epilogue_barrier();
+            if (threadIdx.x == 0) {
+                tma_store_3d(&map_spike, sm.out_spike, m0, b0, 0);
+                if (write_current) tma_store_3d(&map_current, sm.out_current, m0, b0, 0);
+                asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+            }
+        }
+        if (threadIdx.x == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+    }
+
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 5) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
+                     "r"(kTmemColsPersistent)
+                     : "memory");
+    }
+}
+
 // ---- host side ---------------------------------------------------------------------------------
 using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                    const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -269,13 +455,15 @@ EncodeTiledFn encode_tiled() {
     return fn;
 }
 
+// swizzled = operand tiles read by the MMA (128-byte swizzle); plain = output tiles written by TMA stores
 bool make_map(CUtensorMap* map, const void* base, int rank, const cuuint64_t* dims, const cuuint64_t* strides,
-              const cuuint32_t* box) {
+              const cuuint32_t* box, bool swizzled) {
     EncodeTiledFn enc = encode_tiled();
     if (enc == nullptr) return false;
     const cuuint32_t elem_strides[3] = {1, 1, 1};
     return enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, static_cast<cuuint32_t>(rank), const_cast<void*>(base), dims,
-               strides, box, elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+               strides, box, elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE,
+               swizzled ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
                CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
@@ -283,23 +471,23 @@ bool make_map(CUtensorMap* map, const void* base, int rank, const cuuint64_t* di
 // small layers, and a training loop calls with the same buffers step after step: keep the last
 // few maps keyed by everything that went into them.
 struct MapKey {
-    const void* base; int rank; cuuint64_t dims[3]; cuuint32_t box[3];
+    const void* base; int rank; cuuint64_t dims[3]; cuuint32_t box[3]; bool swizzled;
     bool operator==(const MapKey& o) const {
-        if (base != o.base || rank != o.rank) return false;
+        if (base != o.base || rank != o.rank || swizzled != o.swizzled) return false;
         for (int i = 0; i < 3; ++i) if (dims[i] != o.dims[i] || box[i] != o.box[i]) return false;
         return true;
     }
 };
 bool cached_map(CUtensorMap* out, const void* base, int rank, const cuuint64_t* dims, const cuuint64_t* strides,
-                const cuuint32_t* box) {
+                const cuuint32_t* box, bool swizzled = true) {
     constexpr int kSlots = 16;
     thread_local MapKey keys[kSlots];
     thread_local CUtensorMap maps[kSlots];
     thread_local int used = 0, next = 0;
-    MapKey k{base, rank, {dims[0], dims[1], rank > 2 ? dims[2] : 1}, {box[0], box[1], rank > 2 ? box[2] : 1}};
+    MapKey k{base, rank, {dims[0], dims[1], rank > 2 ? dims[2] : 1}, {box[0], box[1], rank > 2 ? box[2] : 1}, swizzled};
     for (int i = 0; i < used; ++i)
         if (keys[i] == k) { *out = maps[i]; return true; }
-    if (!make_map(out, base, rank, dims, strides, box)) return false;
+    if (!make_map(out, base, rank, dims, strides, box, swizzled)) return false;
     const int slot = used < kSlots ? used++ : (next++ % kSlots);
     keys[slot] = k;
     maps[slot] = *out;
@@ -319,6 +507,36 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mx, const float* bias, void
     e = cudaGetLastError();
     if (e != cudaSuccess) { snn_internal::set_last_cuda_error(static_cast<int>(e)); return SNN_ERR_CUDA; }
     return SNN_OK;
+}
+
+template <int T>
+int launch_persistent(const CUtensorMap& mw, const CUtensorMap& mx, const CUtensorMap& ms, const CUtensorMap& mc,
+                      int write_current, const float* bias, int B, int K, int M, float alpha, float thresh,
+                      cudaStream_t st) {
+    const size_t smem = sizeof(PersistentStorage) + 1024;
+    auto kern = linear_lif_fwd_persistent_kernel<T>;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    int dev = 0, sms = 0;
+    if (e == cudaSuccess) e = cudaGetDevice(&dev);
+    if (e == cudaSuccess) e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    if (e != cudaSuccess) { snn_internal::set_last_cuda_error(static_cast<int>(e)); return SNN_ERR_CUDA; }
+    const int tiles = (M / BM) * (B / (BN / T));
+    const int grid = tiles < sms ? tiles : sms;
+    kern<<<grid, kThreads, smem, st>>>(mw, mx, ms, mc, write_current, bias, B, K, M, alpha, thresh);
+    e = cudaGetLastError();
+    if (e != cudaSuccess) { snn_internal::set_last_cuda_error(static_cast<int>(e)); return SNN_ERR_CUDA; }
+    return SNN_OK;
+}
+
+// SNN_LINEAR_LIF_VARIANT=1 selects the one-tile-per-CTA kernel (kept for comparison); default is
+// the persistent kernel.
+int variant() {
+    static int v = -1;
+    if (v < 0) {
+        const char* e = getenv("SNN_LINEAR_LIF_VARIANT");
+        v = (e != nullptr && e[0] == '1') ? 1 : 0;
+    }
+    return v;
 }
 
 }  // namespace
@@ -357,8 +575,23 @@ int snn_linear_lif_fwd(const void* x, const void* weight, const float* bias, voi
     }
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const int Bi = static_cast<int>(B), Ki = static_cast<int>(K), Mi = static_cast<int>(M);
-    if (T == 4) return launch<4>(mw, mx, bias, current, spike, Bi, Ki, Mi, alpha, thresh, st);
-    return launch<8>(mw, mx, bias, current, spike, Bi, Ki, Mi, alpha, thresh, st);
+    if (variant() == 1 || !al(spike, 16) || !al(current, 16)) {
+        if (T == 4) return launch<4>(mw, mx, bias, current, spike, Bi, Ki, Mi, alpha, thresh, st);
+        return launch<8>(mw, mx, bias, current, spike, Bi, Ki, Mi, alpha, thresh, st);
+    }
+    CUtensorMap ms, mc;
+    const cuuint64_t odims[3] = {static_cast<cuuint64_t>(M), static_cast<cuuint64_t>(B), static_cast<cuuint64_t>(T)};
+    const cuuint64_t ostr[2] = {static_cast<cuuint64_t>(M) * 2, static_cast<cuuint64_t>(B) * M * 2};
+    const cuuint32_t obox[3] = {BM, static_cast<cuuint32_t>(BN / T), static_cast<cuuint32_t>(T)};
+    if (!cached_map(&ms, spike, 3, odims, ostr, obox, false) ||
+        (current != nullptr && !cached_map(&mc, current, 3, odims, ostr, obox, false))) {
+        snn_internal::set_last_cuda_error(static_cast<int>(cudaErrorInvalidValue));
+        return SNN_ERR_CUDA;
+    }
+    if (current == nullptr) mc = ms;
+    const int wc = current != nullptr ? 1 : 0;
+    if (T == 4) return launch_persistent<4>(mw, mx, ms, mc, wc, bias, Bi, Ki, Mi, alpha, thresh, st);
+    return launch_persistent<8>(mw, mx, ms, mc, wc, bias, Bi, Ki, Mi, alpha, thresh, st);
 }
 
 int snn_linear_lif_error(int reset) {
