@@ -133,7 +133,7 @@ __global__ void bn_lif_fwd_kernel(const IO* __restrict__ x, IO* __restrict__ out
 // does), run the reverse-time recurrence and hand each gu(t, v) to `emit` as soon as it is
 // known, so no array of gradients has to stay live beside x and u.
 // ---------------------------------------------------------------------------------------
-template <typename IO, int VEC, int TMAX, bool FIRE, typename Emit>
+template <typename IO, int VEC, int TMAX, bool FIRE, bool EXACT, typename Emit>
 __device__ __forceinline__ void bn_lif_grad_current(const Pack<IO, VEC> (&xin)[TMAX],
                                                     const Pack<IO, VEC> (&gin)[TMAX], int T,
                                                     const float (&m)[VEC], const float (&wiv)[VEC],
@@ -143,7 +143,7 @@ __device__ __forceinline__ void bn_lif_grad_current(const Pack<IO, VEC> (&xin)[T
     if constexpr (!FIRE) {
 #pragma unroll
         for (int t = 0; t < TMAX; ++t)
-            if (t < T) {
+            if (EXACT || t < T) {
 #pragma unroll
                 for (int v = 0; v < VEC; ++v) emit(t, v, Elem<IO>::load(gin[t].v[v]));
             }
@@ -154,7 +154,7 @@ __device__ __forceinline__ void bn_lif_grad_current(const Pack<IO, VEC> (&xin)[T
         for (int v = 0; v < VEC; ++v) { uu[v] = 0.f; gate[v] = 1.f; }
 #pragma unroll
         for (int t = 0; t < TMAX; ++t) {
-            if (t < T) {
+            if (EXACT || t < T) {
 #pragma unroll
                 for (int v = 0; v < VEC; ++v) {
                     uu[v] = bn_lif_step(uu[v], gate[v], Elem<IO>::load(xin[t].v[v]), m[v], wiv[v], b[v], alpha);
@@ -168,7 +168,7 @@ __device__ __forceinline__ void bn_lif_grad_current(const Pack<IO, VEC> (&xin)[T
         for (int v = 0; v < VEC; ++v) gu[v] = 0.f;
 #pragma unroll
         for (int t = TMAX - 1; t >= 0; --t) {
-            if (t < T) {
+            if (EXACT || t < T) {
 #pragma unroll
                 for (int v = 0; v < VEC; ++v) {
                     const float ut = u[t][v];
@@ -194,10 +194,11 @@ __device__ __forceinline__ void bn_lif_grad_current(const Pack<IO, VEC> (&xin)[T
 //                     (dynamic shared memory 2*nq floats, nq = (span + inner - 1)/inner + 1),
 //                     then one global atomicAdd pair per (CTA, run).
 // ---------------------------------------------------------------------------------------
-template <typename IO, int VEC, int TMAX, bool FIRE, bool WARP_RUN>
-__global__ void __launch_bounds__(256, (VEC * TMAX <= 16) ? 4 : 1) bn_lif_bwd_sums_kernel(const IO* __restrict__ x, const IO* __restrict__ g,
+// EXACT = (T == TMAX): the time loops then carry no per-step bound checks.
+template <typename IO, int VEC, int TMAX, bool FIRE, bool WARP_RUN, bool EXACT>
+__device__ __forceinline__ void bn_lif_bwd_sums_body(const IO* __restrict__ x, const IO* __restrict__ g,
                                        float* __restrict__ sum_g, float* __restrict__ sum_gx,
-                                       BnParams p, int T, long long N, int nq, float alpha,
+                                       const BnParams& p, int T, long long N, int nq, float alpha,
                                        float thresh, float beta, float interval)
 {
     extern __shared__ float sacc[];                       // [2][nq]   (unused when WARP_RUN)
@@ -230,11 +231,11 @@ __global__ void __launch_bounds__(256, (VEC * TMAX <= 16) ? 4 : 1) bn_lif_bwd_su
         Pack<IO, VEC> xin[TMAX], gin[TMAX];
 #pragma unroll
         for (int t = 0; t < TMAX; ++t)
-            if (t < T) xin[t] = ld_stream<IO, VEC>(x + static_cast<long long>(t) * N + i);
+            if (EXACT || t < T) xin[t] = ld_stream<IO, VEC>(x + static_cast<long long>(t) * N + i);
 #pragma unroll
         for (int t = 0; t < TMAX; ++t)
-            if (t < T) gin[t] = ld_stream<IO, VEC>(g + static_cast<long long>(t) * N + i);
-        bn_lif_grad_current<IO, VEC, TMAX, FIRE>(
+            if (EXACT || t < T) gin[t] = ld_stream<IO, VEC>(g + static_cast<long long>(t) * N + i);
+        bn_lif_grad_current<IO, VEC, TMAX, FIRE, EXACT>(
             xin, gin, T, m, wiv, b, alpha, thresh, beta, interval, [&](int t, int v, float gu) {
                 const float xhat = mul_rn(sub_rn(Elem<IO>::load(xin[t].v[v]), m[v]), iv[v]);
                 s1[v] += gu;
@@ -296,14 +297,26 @@ __global__ void __launch_bounds__(256, (VEC * TMAX <= 16) ? 4 : 1) bn_lif_bwd_su
     }
 }
 
+template <typename IO, int VEC, int TMAX, bool FIRE, bool WARP_RUN>
+__global__ void __launch_bounds__(256, (VEC * TMAX <= 16) ? 4 : ((VEC * TMAX <= 32) ? 2 : 1))
+bn_lif_bwd_sums_kernel(const IO* __restrict__ x, const IO* __restrict__ g, float* __restrict__ sum_g,
+                       float* __restrict__ sum_gx, BnParams p, int T, long long N, int nq, float alpha,
+                       float thresh, float beta, float interval)
+{
+    if (T == TMAX)
+        bn_lif_bwd_sums_body<IO, VEC, TMAX, FIRE, WARP_RUN, true>(x, g, sum_g, sum_gx, p, T, N, nq, alpha, thresh, beta, interval);
+    else
+        bn_lif_bwd_sums_body<IO, VEC, TMAX, FIRE, WARP_RUN, false>(x, g, sum_g, sum_gx, p, T, N, nq, alpha, thresh, beta, interval);
+}
+
 // ---------------------------------------------------------------------------------------
 // Backward pass 2: grad_x = gu*w*ivar - ivar*(xhat*gxhatx[c] + gxhat[c]).
 // ---------------------------------------------------------------------------------------
-template <typename IO, int VEC, int TMAX, bool FIRE>
-__global__ void __launch_bounds__(256, (VEC * TMAX <= 16) ? 4 : 1) bn_lif_bwd_input_kernel(const IO* __restrict__ x, const IO* __restrict__ g,
+template <typename IO, int VEC, int TMAX, bool FIRE, bool EXACT>
+__device__ __forceinline__ void bn_lif_bwd_input_body(const IO* __restrict__ x, const IO* __restrict__ g,
                                         const float* __restrict__ gxhat,
                                         const float* __restrict__ gxhatx, IO* __restrict__ gx,
-                                        BnParams p, int T, long long N, float alpha, float thresh,
+                                        const BnParams& p, int T, long long N, float alpha, float thresh,
                                         float beta, float interval)
 {
     const long long i = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) * VEC;
@@ -328,12 +341,12 @@ __global__ void __launch_bounds__(256, (VEC * TMAX <= 16) ? 4 : 1) bn_lif_bwd_in
     Pack<IO, VEC> xin[TMAX], gin[TMAX];
 #pragma unroll
     for (int t = 0; t < TMAX; ++t)
-        if (t < T) xin[t] = ld_stream<IO, VEC>(x + static_cast<long long>(t) * N + i);
+        if (EXACT || t < T) xin[t] = ld_stream<IO, VEC>(x + static_cast<long long>(t) * N + i);
 #pragma unroll
     for (int t = 0; t < TMAX; ++t)
-        if (t < T) gin[t] = ld_stream<IO, VEC>(g + static_cast<long long>(t) * N + i);
+        if (EXACT || t < T) gin[t] = ld_stream<IO, VEC>(g + static_cast<long long>(t) * N + i);
     Pack<IO, VEC> o;
-    bn_lif_grad_current<IO, VEC, TMAX, FIRE>(
+    bn_lif_grad_current<IO, VEC, TMAX, FIRE, EXACT>(
         xin, gin, T, m, wiv, b, alpha, thresh, beta, interval, [&](int t, int v, float gu) {
             const float xhat = mul_rn(sub_rn(Elem<IO>::load(xin[t].v[v]), m[v]), iv[v]);
             const float lhs = mul_rn(mul_rn(gu, wt[v]), iv[v]);
@@ -341,6 +354,18 @@ __global__ void __launch_bounds__(256, (VEC * TMAX <= 16) ? 4 : 1) bn_lif_bwd_in
             o.v[v] = Elem<IO>::store(sub_rn(lhs, rhs));
             if (v == VEC - 1) st_stream<IO, VEC>(gx + static_cast<long long>(t) * N + i, o);   // row t complete
         });
+}
+
+template <typename IO, int VEC, int TMAX, bool FIRE>
+__global__ void __launch_bounds__(256, (VEC * TMAX <= 16) ? 4 : ((VEC * TMAX <= 32) ? 2 : 1))
+bn_lif_bwd_input_kernel(const IO* __restrict__ x, const IO* __restrict__ g, const float* __restrict__ gxhat,
+                        const float* __restrict__ gxhatx, IO* __restrict__ gx, BnParams p, int T, long long N,
+                        float alpha, float thresh, float beta, float interval)
+{
+    if (T == TMAX)
+        bn_lif_bwd_input_body<IO, VEC, TMAX, FIRE, true>(x, g, gxhat, gxhatx, gx, p, T, N, alpha, thresh, beta, interval);
+    else
+        bn_lif_bwd_input_body<IO, VEC, TMAX, FIRE, false>(x, g, gxhat, gxhatx, gx, p, T, N, alpha, thresh, beta, interval);
 }
 
 // gxhat[c] = weight[c]*sum_g[c]/count ; gxhatx[c] = weight[c]*sum_gx[c]/count  (C threads)

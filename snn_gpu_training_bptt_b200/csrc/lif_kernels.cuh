@@ -164,11 +164,12 @@ __device__ __forceinline__ void store_words(void* bits, int64_t i, const unsigne
     st_stream<W, VEC>(reinterpret_cast<W*>(bits) + i, w);
 }
 
-template <typename IO, int VEC, int TC>
-__global__ void lif_fwd_kernel(const IO* __restrict__ x, IO* __restrict__ spike,
-                               typename Elem<IO>::CT* __restrict__ mem,
-                               void* __restrict__ bits, int word_bytes, int T, int64_t N,
-                               float alpha_f, float thresh_f)
+// EXACT = T is a multiple of TC (no per-step bound checks); BITS = packed words requested.
+template <typename IO, int VEC, int TC, bool EXACT, bool BITS>
+__device__ __forceinline__ void lif_fwd_body(const IO* __restrict__ x, IO* __restrict__ spike,
+                                             typename Elem<IO>::CT* __restrict__ mem,
+                                             void* __restrict__ bits, int word_bytes, int T, int64_t N,
+                                             float alpha_f, float thresh_f)
 {
     using CT = typename Elem<IO>::CT;
     const int64_t i = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) * VEC;
@@ -184,10 +185,10 @@ __global__ void lif_fwd_kernel(const IO* __restrict__ x, IO* __restrict__ spike,
         Pack<IO, VEC> xin[TC];
 #pragma unroll
         for (int k = 0; k < TC; ++k)
-            if (t0 + k < T) xin[k] = ld_stream<IO, VEC>(x + static_cast<int64_t>(t0 + k) * N + i);
+            if (EXACT || t0 + k < T) xin[k] = ld_stream<IO, VEC>(x + static_cast<int64_t>(t0 + k) * N + i);
 #pragma unroll
         for (int k = 0; k < TC; ++k) {
-            if (t0 + k < T) {
+            if (EXACT || t0 + k < T) {
                 Pack<IO, VEC> sp;
                 Pack<CT, VEC> mm;
 #pragma unroll
@@ -198,7 +199,7 @@ __global__ void lif_fwd_kernel(const IO* __restrict__ x, IO* __restrict__ spike,
                     gate[v] = s ? CT(0) : CT(1);
                     sp.v[v] = Elem<IO>::store(s ? CT(1) : CT(0));
                     mm.v[v] = u[v];
-                    word[v] |= (s ? 1u : 0u) << ((t0 + k) & 31);
+                    if (BITS) word[v] |= (s ? 1u : 0u) << ((t0 + k) & 31);
                 }
                 const int64_t off = static_cast<int64_t>(t0 + k) * N + i;
                 if (spike != nullptr) st_stream<IO, VEC>(spike + off, sp);
@@ -206,11 +207,25 @@ __global__ void lif_fwd_kernel(const IO* __restrict__ x, IO* __restrict__ spike,
             }
         }
     }
-    if (bits != nullptr) {
+    if (BITS) {
         if (word_bytes == 1) store_words<unsigned char, VEC>(bits, i, word);
         else if (word_bytes == 2) store_words<unsigned short, VEC>(bits, i, word);
         else store_words<unsigned int, VEC>(bits, i, word);
     }
+}
+
+template <typename IO, int VEC, int TC>
+__global__ void lif_fwd_kernel(const IO* __restrict__ x, IO* __restrict__ spike,
+                               typename Elem<IO>::CT* __restrict__ mem,
+                               void* __restrict__ bits, int word_bytes, int T, int64_t N,
+                               float alpha_f, float thresh_f)
+{
+    if (bits != nullptr)
+        lif_fwd_body<IO, VEC, TC, false, true>(x, spike, mem, bits, word_bytes, T, N, alpha_f, thresh_f);
+    else if (T % TC == 0)
+        lif_fwd_body<IO, VEC, TC, true, false>(x, spike, mem, bits, word_bytes, T, N, alpha_f, thresh_f);
+    else
+        lif_fwd_body<IO, VEC, TC, false, false>(x, spike, mem, bits, word_bytes, T, N, alpha_f, thresh_f);
 }
 
 // ---------------------------------------------------------------------------------------
@@ -218,10 +233,10 @@ __global__ void lif_fwd_kernel(const IO* __restrict__ x, IO* __restrict__ spike,
 // loads in flight per thread), rebuilds u_t in registers, then walks time in reverse and
 // stores grad_x. No membrane tensor is read or written.
 // ---------------------------------------------------------------------------------------
-template <typename IO, int VEC, int TMAX>
-__global__ void lif_bwd_kernel(const IO* __restrict__ x, const IO* __restrict__ g,
-                               IO* __restrict__ gx, int T, int64_t N, float alpha_f,
-                               float thresh_f, float beta_f, float interval_f)
+template <typename IO, int VEC, int TMAX, bool EXACT>
+__device__ __forceinline__ void lif_bwd_body(const IO* __restrict__ x, const IO* __restrict__ g,
+                                             IO* __restrict__ gx, int T, int64_t N, float alpha_f,
+                                             float thresh_f, float beta_f, float interval_f)
 {
     using CT = typename Elem<IO>::CT;
     const int64_t i = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) * VEC;
@@ -232,10 +247,10 @@ __global__ void lif_bwd_kernel(const IO* __restrict__ x, const IO* __restrict__ 
     Pack<IO, VEC> xin[TMAX], gin[TMAX];
 #pragma unroll
     for (int t = 0; t < TMAX; ++t)
-        if (t < T) xin[t] = ld_stream<IO, VEC>(x + static_cast<int64_t>(t) * N + i);
+        if (EXACT || t < T) xin[t] = ld_stream<IO, VEC>(x + static_cast<int64_t>(t) * N + i);
 #pragma unroll
     for (int t = 0; t < TMAX; ++t)
-        if (t < T) gin[t] = ld_stream<IO, VEC>(g + static_cast<int64_t>(t) * N + i);
+        if (EXACT || t < T) gin[t] = ld_stream<IO, VEC>(g + static_cast<int64_t>(t) * N + i);
 
     CT u[TMAX][VEC];
     {
@@ -244,7 +259,7 @@ __global__ void lif_bwd_kernel(const IO* __restrict__ x, const IO* __restrict__ 
         for (int v = 0; v < VEC; ++v) { uu[v] = CT(0); gate[v] = CT(1); }
 #pragma unroll
         for (int t = 0; t < TMAX; ++t) {
-            if (t < T) {
+            if (EXACT || t < T) {
 #pragma unroll
                 for (int v = 0; v < VEC; ++v) {
                     CT leak = mul_rn(mul_rn(alpha, uu[v]), gate[v]);
@@ -261,7 +276,7 @@ __global__ void lif_bwd_kernel(const IO* __restrict__ x, const IO* __restrict__ 
     for (int v = 0; v < VEC; ++v) gu[v] = CT(0);
 #pragma unroll
     for (int t = TMAX - 1; t >= 0; --t) {
-        if (t < T) {
+        if (EXACT || t < T) {
             Pack<IO, VEC> out;
 #pragma unroll
             for (int v = 0; v < VEC; ++v) {
@@ -280,6 +295,23 @@ __global__ void lif_bwd_kernel(const IO* __restrict__ x, const IO* __restrict__ 
 }
 
 // ---------------------------------------------------------------------------------------
+// T == TMAX (the common case: 4, 6, 8, 12, 16 steps) runs without per-step bound checks.
+template <typename IO, int VEC, int TMAX>
+__global__ void
+lif_bwd_kernel(const IO* __restrict__ x, const IO* __restrict__ g,
+               IO* __restrict__ gx, int T, int64_t N, float alpha_f,
+               float thresh_f, float beta_f, float interval_f)
+{
+    // Two bodies in one kernel cost registers; where that drops a resident block (16-bit I/O,
+    // 4 x 16 values per thread: 114 -> 140 registers) only the checked body is compiled.
+    constexpr bool kSpecialise = !(sizeof(IO) == 2 && VEC * TMAX >= 64 && TMAX >= 16);
+    if (kSpecialise && T == TMAX)
+        lif_bwd_body<IO, VEC, TMAX, true>(x, g, gx, T, N, alpha_f, thresh_f, beta_f, interval_f);
+    else
+        lif_bwd_body<IO, VEC, TMAX, false>(x, g, gx, T, N, alpha_f, thresh_f, beta_f, interval_f);
+}
+
+
 // Backward for long T (beyond what fits in registers): reads a stored membrane tensor
 // (written by lif_fwd_kernel's `mem` output into caller-provided scratch) and walks time in
 // reverse in chunks of TC steps. Same arithmetic as above.
