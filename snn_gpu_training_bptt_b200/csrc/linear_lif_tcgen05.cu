@@ -17,7 +17,8 @@
 // carries u / gate of its 128/T batch items in registers across the T loads.
 //
 // Two kernels share the pieces below: a one-tile-per-CTA version and, the default, a persistent
-// version (further down) that overlaps the epilogue of one tile with the MMAs of the next.
+// version (further down) that overlaps the epilogue of one tile with the MMAs of the next and can
+// use 128 x 256 tiles (2 x 128/T batch items per tile) to halve the W traffic per flop.
 //
 // Pipeline (192 threads): warp 4 = TMA producer (one lane), warp 5 = MMA issuer (one lane, also
 // owns the TMEM allocation), warps 0-3 = epilogue (128 lanes of TMEM). STAGES shared-memory
@@ -258,20 +259,31 @@ linear_lif_fwd_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
 
 // ---------------------------------------------------------------------------------------------
 // Persistent variant: one CTA per SM walks a strided list of output tiles. Two accumulators in
-// tensor memory (2 x 128 columns) let the LIF epilogue of tile i run while the MMAs of tile i+1
+// tensor memory (2 x WN columns) let the LIF epilogue of tile i run while the MMAs of tile i+1
 // fill the other one; the epilogue writes its bf16 currents / spikes into a shared-memory tile
 // laid out [t][b][m] and hands it to one 3-D TMA store per output instead of 2-byte stores.
+//
+// WN = accumulator columns per tile, 128 or 256. The mainloop is bound by what one SM can pull
+// from L2 (measured ~58 B/clk against 128 B/clk needed to feed 128x128x64 MMAs at full rate);
+// a 128 x 256 tile moves 48 KB per stage for twice the flops of a 128 x 128 tile's 32 KB, so
+// the wide tile is used when it does not cost a wave of parallelism (see pick_wide()). The
+// epilogue handles a wide tile as two 128-column chunks through the same staging buffers.
 // ---------------------------------------------------------------------------------------------
-constexpr int PSTAGES = 4;
-constexpr uint32_t kTmemColsPersistent = 256;
+template <int WN> struct PersistentCfg {
+    static constexpr int kStages = WN == 128 ? 4 : 3;             // 4 x 32 KB or 3 x 48 KB in flight
+    static constexpr uint32_t kTmemCols = 2 * WN;                 // two accumulators
+    static constexpr uint32_t kStageBytesB = WN * BK * 2;
+};
 
+template <int WN>
 struct __align__(1024) PersistentStorage {
-    __nv_bfloat16 a[PSTAGES][BM * BK];
-    __nv_bfloat16 b[PSTAGES][BN * BK];
-    __nv_bfloat16 out_spike[BN * BM];      // [n = t*BT + j][m]
-    __nv_bfloat16 out_current[BN * BM];
-    uint64_t full[PSTAGES];
-    uint64_t empty[PSTAGES];
+    static constexpr int kStages = PersistentCfg<WN>::kStages;
+    __nv_bfloat16 a[kStages][BM * BK];
+    __nv_bfloat16 b[kStages][WN * BK];
+    __nv_bfloat16 out_spike[128 * BM];     // one 128-column chunk: [n = t*(128/T) + j][m]
+    __nv_bfloat16 out_current[128 * BM];
+    uint64_t full[kStages];
+    uint64_t empty[kStages];
     uint64_t acc_full[2];
     uint64_t acc_empty[2];
     uint32_t tmem_base;
@@ -288,16 +300,19 @@ __device__ __forceinline__ void tma_store_3d(const CUtensorMap* map, const void*
 }
 __device__ __forceinline__ void epilogue_barrier() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
 
-template <int T>
+template <int T, int WN>
 __global__ void __launch_bounds__(kThreads, 1)
 linear_lif_fwd_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                                  const __grid_constant__ CUtensorMap map_spike,
                                  const __grid_constant__ CUtensorMap map_current, int write_current,
                                  const float* __restrict__ bias, int B, int K, int M, float alpha, float thresh)
 {
-    constexpr int BT = BN / T;
+    constexpr int BT = WN / T;                  // batch items per tile
+    constexpr int CB = 128 / T;                 // batch items per 128-column epilogue chunk
+    constexpr int PSTAGES = PersistentCfg<WN>::kStages;
+    constexpr uint32_t kTmemColsPersistent = PersistentCfg<WN>::kTmemCols;
     extern __shared__ __align__(1024) unsigned char smem_raw[];
-    PersistentStorage& sm = *reinterpret_cast<PersistentStorage*>(
+    PersistentStorage<WN>& sm = *reinterpret_cast<PersistentStorage<WN>*>(
         (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -335,7 +350,7 @@ linear_lif_fwd_persistent_kernel(const __grid_constant__ CUtensorMap map_w, cons
                     const int s = it % PSTAGES;
                     const uint32_t parity = ((it / PSTAGES) & 1) ^ 1;
                     if (!mbar_wait(&sm.empty[s], parity)) { atomicExch(&g_linear_lif_error, 1); ok = false; break; }
-                    mbar_expect_tx(&sm.full[s], kStageBytesA + kStageBytesB);
+                    mbar_expect_tx(&sm.full[s], kStageBytesA + PersistentCfg<WN>::kStageBytesB);
                     tma_load_2d(sm.a[s], &map_w, &sm.full[s], kb * BK, m0);
                     tma_load_3d(sm.b[s], &map_x, &sm.full[s], kb * BK, b0, 0);
                 }
@@ -344,7 +359,7 @@ linear_lif_fwd_persistent_kernel(const __grid_constant__ CUtensorMap map_w, cons
     } else if (warp == 5) {
         // ------------------------------ MMA issuer --------------------------------
         if (lane == 0) {
-            constexpr uint32_t idesc = umma_idesc_bf16(BM, BN);
+            constexpr uint32_t idesc = umma_idesc_bf16(BM, WN);
             int it = 0, local = 0;
             bool ok = true;
             for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
@@ -352,7 +367,7 @@ linear_lif_fwd_persistent_kernel(const __grid_constant__ CUtensorMap map_w, cons
                 const uint32_t acc_parity = ((local >> 1) & 1) ^ 1;      // first use of a buffer passes
                 if (!mbar_wait(&sm.acc_empty[buf], acc_parity)) { atomicExch(&g_linear_lif_error, 4); break; }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint32_t tmem_acc = tmem_base + buf * BN;
+                const uint32_t tmem_acc = tmem_base + buf * WN;
                 for (int kb = 0; kb < num_kb; ++kb, ++it) {
                     const int s = it % PSTAGES;
                     const uint32_t parity = (it / PSTAGES) & 1;
@@ -389,41 +404,52 @@ linear_lif_fwd_persistent_kernel(const __grid_constant__ CUtensorMap map_w, cons
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 
             const float bias_m = bias != nullptr ? bias[m0 + row] : 0.f;
-            float u[BT], gate[BT];
+            const uint32_t lane_base = tmem_base + buf * WN + (static_cast<uint32_t>(warp * 32) << 16);
 #pragma unroll
-            for (int j = 0; j < BT; ++j) { u[j] = 0.f; gate[j] = 1.f; }
-            const uint32_t lane_base = tmem_base + buf * BN + (static_cast<uint32_t>(warp * 32) << 16);
+            for (int h = 0; h < WN / 128; ++h) {          // 128-column chunk = CB batch items x T steps
+                if (h > 0) {
+                    // the previous chunk's TMA stores must have finished reading the staging tiles
+                    if (threadIdx.x == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+                    epilogue_barrier();
+                }
+                float u[CB], gate[CB];
 #pragma unroll
-            for (int t = 0; t < T; ++t) {
+                for (int j = 0; j < CB; ++j) { u[j] = 0.f; gate[j] = 1.f; }
 #pragma unroll
-                for (int c = 0; c < BT; c += 16) {
-                    uint32_t r[16];
-                    tmem_ld16(lane_base + t * BT + c, r);
-                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                for (int t = 0; t < T; ++t) {
 #pragma unroll
-                    for (int j = 0; j < 16; ++j) {
-                        const __nv_bfloat16 cur_h = __float2bfloat16_rn(__fadd_rn(__uint_as_float(r[j]), bias_m));
-                        const float cur = __bfloat162float(cur_h);
-                        const float leak = __fmul_rn(__fmul_rn(alpha, u[c + j]), gate[c + j]);
-                        u[c + j] = __fadd_rn(leak, cur);
-                        const bool s = u[c + j] > thresh;
-                        gate[c + j] = s ? 0.f : 1.f;
-                        const int n = t * BT + c + j;
-                        sm.out_spike[n * BM + row] = __float2bfloat16_rn(s ? 1.f : 0.f);
-                        sm.out_current[n * BM + row] = cur_h;
+                    for (int c = 0; c < CB; c += 16) {
+                        uint32_t r[16];
+                        tmem_ld16(lane_base + t * BT + h * CB + c, r);
+                        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) {
+                            const __nv_bfloat16 cur_h =
+                                __float2bfloat16_rn(__fadd_rn(__uint_as_float(r[j]), bias_m));
+                            const float cur = __bfloat162float(cur_h);
+                            const float leak = __fmul_rn(__fmul_rn(alpha, u[c + j]), gate[c + j]);
+                            u[c + j] = __fadd_rn(leak, cur);
+                            const bool s = u[c + j] > thresh;
+                            gate[c + j] = s ? 0.f : 1.f;
+                            const int n = t * CB + c + j;
+                            sm.out_spike[n * BM + row] = __float2bfloat16_rn(s ? 1.f : 0.f);
+                            sm.out_current[n * BM + row] = cur_h;
+                        }
                     }
                 }
-            }
-            // accumulator drained: hand the TMEM buffer back to the MMA warp
-            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-            mbar_arrive(&sm.acc_empty[buf]);
-            // staging tiles complete: one thread issues the bulk stores
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-            epilogue_barrier();
-            if (threadIdx.x == 0) {
-                tma_store_3d(&map_spike, sm.out_spike, m0, b0, 0);
-                if (write_current) tma_store_3d(&map_current, sm.out_current, m0, b0, 0);
-                asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+                if (h == WN / 128 - 1) {
+                    // accumulator drained: hand the TMEM buffer back to the MMA warp
+                    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                    mbar_arrive(&sm.acc_empty[buf]);
+                }
+                // staging tiles complete: one thread issues the bulk stores
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                epilogue_barrier();
+                if (threadIdx.x == 0) {
+                    tma_store_3d(&map_spike, sm.out_spike, m0, b0 + h * CB, 0);
+                    if (write_current) tma_store_3d(&map_current, sm.out_current, m0, b0 + h * CB, 0);
+                    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+                }
             }
         }
         if (threadIdx.x == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
@@ -509,18 +535,29 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mx, const float* bias, void
     return SNN_OK;
 }
 
-template <int T>
+int sm_count() {
+    thread_local int dev_cached = -1, sms = 0;
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return 0;
+    if (dev != dev_cached) {
+        if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return 0;
+        dev_cached = dev;
+    }
+    return sms;
+}
+
+template <int T, int WN>
 int launch_persistent(const CUtensorMap& mw, const CUtensorMap& mx, const CUtensorMap& ms, const CUtensorMap& mc,
                       int write_current, const float* bias, int B, int K, int M, float alpha, float thresh,
                       cudaStream_t st) {
-    const size_t smem = sizeof(PersistentStorage) + 1024;
-    auto kern = linear_lif_fwd_persistent_kernel<T>;
+    static_assert(sizeof(PersistentStorage<WN>) + 1024 <= 227 * 1024, "shared memory budget");
+    const size_t smem = sizeof(PersistentStorage<WN>) + 1024;
+    auto kern = linear_lif_fwd_persistent_kernel<T, WN>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
-    int dev = 0, sms = 0;
-    if (e == cudaSuccess) e = cudaGetDevice(&dev);
-    if (e == cudaSuccess) e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    const int sms = sm_count();
+    if (e == cudaSuccess && sms <= 0) e = cudaErrorInvalidDevice;
     if (e != cudaSuccess) { snn_internal::set_last_cuda_error(static_cast<int>(e)); return SNN_ERR_CUDA; }
-    const int tiles = (M / BM) * (B / (BN / T));
+    const int tiles = (M / BM) * (B / (WN / T));
     const int grid = tiles < sms ? tiles : sms;
     kern<<<grid, kThreads, smem, st>>>(mw, mx, ms, mc, write_current, bias, B, K, M, alpha, thresh);
     e = cudaGetLastError();
@@ -528,15 +565,33 @@ int launch_persistent(const CUtensorMap& mw, const CUtensorMap& mx, const CUtens
     return SNN_OK;
 }
 
-// SNN_LINEAR_LIF_VARIANT=1 selects the one-tile-per-CTA kernel (kept for comparison); default is
-// the persistent kernel.
+// SNN_LINEAR_LIF_VARIANT: 1 = one-tile-per-CTA kernel (kept for comparison), 2 = persistent kernel
+// with 128-column tiles, 3 = persistent kernel with 256-column tiles where the batch allows;
+// default 0 = persistent kernel, tile width chosen by pick_wide().
 int variant() {
     static int v = -1;
     if (v < 0) {
         const char* e = getenv("SNN_LINEAR_LIF_VARIANT");
-        v = (e != nullptr && e[0] == '1') ? 1 : 0;
+        v = (e != nullptr && e[0] >= '1' && e[0] <= '3') ? e[0] - '0' : 0;
     }
     return v;
+}
+
+// A 256-column tile does twice the work of a 128-column one in about 1.5x the time (48 KB
+// instead of 2 x 32 KB through the SM's L2 port), but halves the tile count: compare the rounds
+// of tiles each choice needs on this device.
+bool pick_wide(int T, int B, int M) {
+    if (B % (256 / T) != 0) return false;
+    const int v = variant();
+    if (v == 2) return false;
+    if (v == 3) return true;
+    const int sms = sm_count();
+    if (sms <= 0) return false;
+    const long long t128 = static_cast<long long>(M / BM) * (B / (128 / T));
+    const long long t256 = t128 / 2;
+    const long long cost128 = 2 * ((t128 + sms - 1) / sms);
+    const long long cost256 = 3 * ((t256 + sms - 1) / sms);
+    return cost256 < cost128;
 }
 
 }  // namespace
@@ -562,20 +617,23 @@ int snn_linear_lif_fwd(const void* x, const void* weight, const float* bias, voi
     auto al = [](const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; };
     if (!al(x, 16) || !al(weight, 16) || !al(spike, 2) || !al(current, 2) || !al(bias, 4)) return SNN_ERR_ALIGN;
 
+    const bool one_tile = variant() == 1 || !al(spike, 16) || !al(current, 16);
+    const bool wide = !one_tile && pick_wide(static_cast<int>(T), static_cast<int>(B), static_cast<int>(M));
+    const cuuint32_t tile_n = wide ? 256 : 128;
     CUtensorMap mw, mx;
     const cuuint64_t wdims[2] = {static_cast<cuuint64_t>(K), static_cast<cuuint64_t>(M)};
     const cuuint64_t wstr[1] = {static_cast<cuuint64_t>(K) * 2};
     const cuuint32_t wbox[2] = {BK, BM};
     const cuuint64_t xdims[3] = {static_cast<cuuint64_t>(K), static_cast<cuuint64_t>(B), static_cast<cuuint64_t>(T)};
     const cuuint64_t xstr[2] = {static_cast<cuuint64_t>(K) * 2, static_cast<cuuint64_t>(B) * K * 2};
-    const cuuint32_t xbox[3] = {BK, static_cast<cuuint32_t>(BN / T), static_cast<cuuint32_t>(T)};
+    const cuuint32_t xbox[3] = {BK, tile_n / static_cast<cuuint32_t>(T), static_cast<cuuint32_t>(T)};
     if (!cached_map(&mw, weight, 2, wdims, wstr, wbox) || !cached_map(&mx, x, 3, xdims, xstr, xbox)) {
         snn_internal::set_last_cuda_error(static_cast<int>(cudaErrorInvalidValue));
         return SNN_ERR_CUDA;
     }
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const int Bi = static_cast<int>(B), Ki = static_cast<int>(K), Mi = static_cast<int>(M);
-    if (variant() == 1 || !al(spike, 16) || !al(current, 16)) {
+    if (one_tile) {
         if (T == 4) return launch<4>(mw, mx, bias, current, spike, Bi, Ki, Mi, alpha, thresh, st);
         return launch<8>(mw, mx, bias, current, spike, Bi, Ki, Mi, alpha, thresh, st);
     }
@@ -590,8 +648,12 @@ int snn_linear_lif_fwd(const void* x, const void* weight, const float* bias, voi
     }
     if (current == nullptr) mc = ms;
     const int wc = current != nullptr ? 1 : 0;
-    if (T == 4) return launch_persistent<4>(mw, mx, ms, mc, wc, bias, Bi, Ki, Mi, alpha, thresh, st);
-    return launch_persistent<8>(mw, mx, ms, mc, wc, bias, Bi, Ki, Mi, alpha, thresh, st);
+    if (wide) {
+        if (T == 4) return launch_persistent<4, 256>(mw, mx, ms, mc, wc, bias, Bi, Ki, Mi, alpha, thresh, st);
+        return launch_persistent<8, 256>(mw, mx, ms, mc, wc, bias, Bi, Ki, Mi, alpha, thresh, st);
+    }
+    if (T == 4) return launch_persistent<4, 128>(mw, mx, ms, mc, wc, bias, Bi, Ki, Mi, alpha, thresh, st);
+    return launch_persistent<8, 128>(mw, mx, ms, mc, wc, bias, Bi, Ki, Mi, alpha, thresh, st);
 }
 
 int snn_linear_lif_error(int reset) {

@@ -4,6 +4,10 @@ Parity: the LIF input currents against an fp32 GEMM of the same bf16 operands (b
 within one bf16 ulp: only the fp32 summation order differs); the spikes against the CPU oracle
 run on the kernel's own currents (bit-exact); gradients of the FcFire op against the unfused
 fc -> fire composition."""
+import os
+import subprocess
+import sys
+
 import numpy as np
 import pytest
 import torch
@@ -33,8 +37,13 @@ def make(T, B, K, M, seed):
     return x.cuda(), w.cuda(), b.cuda()
 
 
-@pytest.mark.parametrize("shape", [(8, 16, 64, 128), (8, 32, 256, 256), (4, 32, 128, 128), (8, 48, 1024, 384),
-                                   (4, 64, 512, 128), (8, 256, 2048, 2048)])
+# The last three shapes are large enough for the 256-column tiles (the second of them gives every
+# CTA several wide tiles, the third is T=4 with 64 batch items per tile).
+SHAPES = [(8, 16, 64, 128), (8, 32, 256, 256), (4, 32, 128, 128), (8, 48, 1024, 384), (4, 64, 512, 128),
+          (8, 256, 2048, 2048), (8, 1024, 128, 2048), (4, 1024, 256, 2048)]
+
+
+@pytest.mark.parametrize("shape", SHAPES)
 def test_fused_forward_against_reference_gemm_and_oracle(capi, shape):
     T, B, K, M = shape
     x, w, b = make(T, B, K, M, seed=sum(shape))
@@ -56,6 +65,22 @@ def test_fused_forward_against_reference_gemm_and_oracle(capi, shape):
     s_ref2, _ = orc.c_lif_fwd(cur2.float().cpu().numpy())
     assert float((spike2.float().cpu() != torch.from_numpy(s_ref2)).float().mean()) < 2e-3
     assert capi.linear_lif_error() == 0
+
+
+@pytest.mark.parametrize("variant", ["1", "2", "3"])
+def test_each_kernel_variant_passes_the_forward_checks(capi, variant):
+    """The library picks a kernel per problem; the environment switch forces the one-tile kernel (1),
+    128-column persistent tiles (2) or 256-column persistent tiles wherever the batch allows (3). It
+    is read once per process, so each forced variant runs the forward test in a child process."""
+    if os.environ.get("SNN_LINEAR_LIF_VARIANT"):
+        pytest.skip("already inside a forced-variant run")
+    env = dict(os.environ, SNN_LINEAR_LIF_VARIANT=variant)
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    out = subprocess.run([sys.executable, "-m", "pytest", "-x", "-q", "-m", "gpu", "-p", "no:cacheprovider",
+                          os.path.join("tests", "test_linear_lif_gpu.py"), "-k", "fused_forward"],
+                         cwd=root, env=env, capture_output=True, text=True, timeout=600)
+    assert out.returncode == 0, out.stdout[-2000:] + out.stderr[-2000:]
+    assert "%d passed" % len(SHAPES) in out.stdout, out.stdout[-500:]
 
 
 def test_unsupported_problems_are_reported(capi):
