@@ -20,8 +20,9 @@
 // version (further down) that overlaps the epilogue of one tile with the MMAs of the next and can
 // use 128 x 256 tiles (2 x 128/T batch items per tile) to halve the W traffic per flop.
 //
-// Pipeline (192 threads): warp 4 = TMA producer (one lane), warp 5 = MMA issuer (one lane, also
-// owns the TMEM allocation), warps 0-3 = epilogue (128 lanes of TMEM). STAGES shared-memory
+// Pipeline (192 threads; the persistent kernels add a second epilogue group, warps 6-9): warp 4 =
+// TMA producer (one lane), warp 5 = MMA issuer (one lane, also owns the TMEM allocation), warps
+// 0-3 = epilogue (128 lanes of TMEM). STAGES shared-memory
 // stages of {W tile 128x64, X tile 128x64} bf16 with 128-byte swizzle; full/empty mbarriers per
 // stage; tcgen05.commit frees a stage when the MMAs that read it retire and finally signals the
 // accumulator. Every mbarrier wait is bounded (~1 s): on expiry the thread records an error code
@@ -269,6 +270,16 @@ linear_lif_fwd_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
 // the wide tile is used when it does not cost a wave of parallelism (see pick_wide()). The
 // epilogue handles a wide tile as two 128-column chunks through the same staging buffers.
 // ---------------------------------------------------------------------------------------------
+// Threads of the persistent and pair kernels: warps 0-3 = epilogue group 0, warp 4 = TMA producer,
+// warp 5 = MMA issuer / TMEM owner, warps 6-9 = epilogue group 1. A warp may only touch the TMEM
+// lanes of its quarter (warp index mod 4), so the two groups split a tile by columns: it is cut
+// into 32-column units (32/T batch items x T steps) and group g takes units g, g+2, ...
+constexpr int kThreadsP = 320;
+struct EpilogueStaging {                   // one 32-column unit: [n = t*(32/T) + j][m], 2 x 8 KB
+    __nv_bfloat16 spike[32 * BM];
+    __nv_bfloat16 current[32 * BM];
+};
+
 template <int WN> struct PersistentCfg {
     static constexpr int kStages = WN == 128 ? 4 : 3;             // 4 x 32 KB or 3 x 48 KB in flight
     static constexpr uint32_t kTmemCols = 2 * WN;                 // two accumulators
@@ -280,14 +291,13 @@ struct __align__(1024) PersistentStorage {
     static constexpr int kStages = PersistentCfg<WN>::kStages;
     __nv_bfloat16 a[kStages][BM * BK];
     __nv_bfloat16 b[kStages][WN * BK];
-    __nv_bfloat16 out_spike[128 * BM];     // one 128-column chunk: [n = t*(128/T) + j][m]
-    __nv_bfloat16 out_current[128 * BM];
+    EpilogueStaging epi[2][2];             // [epilogue group][double buffer]
     uint64_t full[kStages];
     uint64_t empty[kStages];
     uint64_t acc_full[2];
     uint64_t acc_empty[2];
     uint32_t tmem_base;
-    uint32_t epi_ok;
+    uint32_t epi_ok[2];
 };
 
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
@@ -298,17 +308,113 @@ __device__ __forceinline__ void tma_store_3d(const CUtensorMap* map, const void*
                  "r"(smem_u32(src)), "r"(c0), "r"(c1), "r"(c2)
                  : "memory");
 }
-__device__ __forceinline__ void epilogue_barrier() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+__device__ __forceinline__ void group_barrier(int g) {      // the 128 threads of epilogue group g
+    asm volatile("bar.sync %0, 128;" ::"r"(1 + g) : "memory");
+}
+
+// tcgen05.ld of NCOL (4 or 8) consecutive columns of this warp's 32 lanes into r[0..NCOL)
+template <int NCOL>
+__device__ __forceinline__ void tmem_ld_cols(uint32_t taddr, uint32_t* r) {
+    if constexpr (NCOL == 8) {
+        asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+                     : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+                     : "r"(taddr));
+    } else {
+        static_assert(NCOL == 4, "4 or 8 columns");
+        asm volatile("tcgen05.ld.sync.aligned.32x32b.x4.b32 {%0, %1, %2, %3}, [%4];"
+                     : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                     : "r"(taddr));
+    }
+}
+// Waits for the loads issued so far. The 32 registers of a unit are passed through the statement
+// so that no use of them can be scheduled ahead of the wait.
+__device__ __forceinline__ void tmem_ld_wait32(uint32_t (&r)[32]) {
+    asm volatile("tcgen05.wait::ld.sync.aligned;"
+                 : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]),
+                   "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]),
+                   "+r"(r[15]), "+r"(r[16]), "+r"(r[17]), "+r"(r[18]), "+r"(r[19]), "+r"(r[20]), "+r"(r[21]),
+                   "+r"(r[22]), "+r"(r[23]), "+r"(r[24]), "+r"(r[25]), "+r"(r[26]), "+r"(r[27]), "+r"(r[28]),
+                   "+r"(r[29]), "+r"(r[30]), "+r"(r[31])
+                 :
+                 : "memory");
+}
+
+// LIF epilogue of one accumulator tile for epilogue group g (thread = TMEM lane = output neuron
+// `row` of the tile). The group walks its 32-column units (32/T batch items x all T steps = 32
+// accumulator values per thread): the unit's TMEM loads are issued one unit ahead of the
+// arithmetic; u / gate of the unit's batch items live in registers across its T steps; currents
+// and spikes are staged [t][b][m] in one of the group's two staging buffers and written by one
+// 3-D TMA store each, issued by the group's elected thread, so the store of one unit is read out
+// of shared memory while the next unit is computed into the other buffer. `k` counts the units
+// this group has staged since the kernel started (buffer = k & 1). `drained()` is called by every
+// thread once its last TMEM read of the tile has completed. On entry the accumulator is full.
+template <int T, int WN, typename Drained>
+__device__ __forceinline__ void lif_epilogue_tile(EpilogueStaging (&stage)[2], int& k, int g, bool elected,
+                                                  uint32_t lane_base, int row, float bias_m, float alpha,
+                                                  float thresh, const CUtensorMap* map_spike,
+                                                  const CUtensorMap* map_current, int write_current, int m0,
+                                                  int b0, Drained&& drained)
+{
+    constexpr int BT = WN / T;                  // batch items per tile
+    constexpr int SB = 32 / T;                  // batch items per unit
+    constexpr int PER_GROUP = WN / 64;          // units per group and tile
+    uint32_t r[2][32] = {};
+#pragma unroll
+    for (int t = 0; t < T; ++t) tmem_ld_cols<SB>(lane_base + t * BT + g * SB, &r[0][t * SB]);
+#pragma unroll
+    for (int i = 0; i < PER_GROUP; ++i) {
+        const int q = g + 2 * i;                // unit index inside the tile
+        tmem_ld_wait32(r[i & 1]);
+        if (i + 1 < PER_GROUP) {
+#pragma unroll
+            for (int t = 0; t < T; ++t) tmem_ld_cols<SB>(lane_base + t * BT + (q + 2) * SB, &r[(i + 1) & 1][t * SB]);
+        } else {
+            // accumulator drained: hand the TMEM buffer back to the MMA issuer
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            drained();
+        }
+        // this buffer's previous store was waited for before the group barrier of the unit before
+        EpilogueStaging& st = stage[k & 1];
+        float u[SB], gate[SB];
+#pragma unroll
+        for (int j = 0; j < SB; ++j) { u[j] = 0.f; gate[j] = 1.f; }
+#pragma unroll
+        for (int t = 0; t < T; ++t) {
+#pragma unroll
+            for (int j = 0; j < SB; ++j) {
+                const int n = t * SB + j;
+                const __nv_bfloat16 cur_h = __float2bfloat16_rn(__fadd_rn(__uint_as_float(r[i & 1][n]), bias_m));
+                const float cur = __bfloat162float(cur_h);
+                const float leak = __fmul_rn(__fmul_rn(alpha, u[j]), gate[j]);
+                u[j] = __fadd_rn(leak, cur);
+                const bool s = u[j] > thresh;
+                gate[j] = s ? 0.f : 1.f;
+                st.spike[n * BM + row] = __float2bfloat16_rn(s ? 1.f : 0.f);
+                st.current[n * BM + row] = cur_h;
+            }
+        }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        // the other buffer's store (issued a unit ago) must have been read before anyone passes
+        // the barrier and starts the next unit in it
+        if (elected) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+        group_barrier(g);
+        if (elected) {
+            tma_store_3d(map_spike, st.spike, m0, b0 + q * SB, 0);
+            if (write_current) tma_store_3d(map_current, st.current, m0, b0 + q * SB, 0);
+            asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+        }
+        ++k;
+    }
+}
 
 template <int T, int WN>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(kThreadsP, 1)
 linear_lif_fwd_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                                  const __grid_constant__ CUtensorMap map_spike,
                                  const __grid_constant__ CUtensorMap map_current, int write_current,
                                  const float* __restrict__ bias, int B, int K, int M, float alpha, float thresh)
 {
     constexpr int BT = WN / T;                  // batch items per tile
-    constexpr int CB = 128 / T;                 // batch items per 128-column epilogue chunk
     constexpr int PSTAGES = PersistentCfg<WN>::kStages;
     constexpr uint32_t kTmemColsPersistent = PersistentCfg<WN>::kTmemCols;
     extern __shared__ __align__(1024) unsigned char smem_raw[];
@@ -322,7 +428,7 @@ linear_lif_fwd_persistent_kernel(const __grid_constant__ CUtensorMap map_w, cons
 
     if (threadIdx.x == 4 * 32) {
         for (int s = 0; s < PSTAGES; ++s) { mbar_init(&sm.full[s], 1); mbar_init(&sm.empty[s], 1); }
-        for (int i = 0; i < 2; ++i) { mbar_init(&sm.acc_full[i], 1); mbar_init(&sm.acc_empty[i], 128); }
+        for (int i = 0; i < 2; ++i) { mbar_init(&sm.acc_full[i], 1); mbar_init(&sm.acc_empty[i], 256); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(&map_x) : "memory");
@@ -384,75 +490,35 @@ linear_lif_fwd_persistent_kernel(const __grid_constant__ CUtensorMap map_w, cons
             }
         }
     } else {
-        // ------------------------------ epilogue warps 0-3 ------------------------
-        const int row = warp * 32 + lane;                 // TMEM lane = output neuron inside the tile
-        int local = 0;
+        // ------------------------------ epilogue groups (warps 0-3, 6-9) ----------
+        const int g = warp >= 6 ? 1 : 0;
+        const int quarter = warp & 3;                     // the TMEM lanes this warp may touch
+        const int row = quarter * 32 + lane;              // TMEM lane = output neuron inside the tile
+        const bool elected = lane == 0 && warp == (g ? 6 : 0);
+        int local = 0, staged = 0;
         for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++local) {
             const int m0 = (tile % tiles_m) * BM, b0 = (tile / tiles_m) * BT;
             const int buf = local & 1;
             const uint32_t acc_parity = (local >> 1) & 1;
-            if (threadIdx.x == 0) {
+            if (elected) {
                 const bool ok0 = mbar_wait(&sm.acc_full[buf], acc_parity);
                 if (!ok0) atomicExch(&g_linear_lif_error, 3);
-                // the previous tile's TMA stores must have finished reading the staging tiles
-                asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
-                sm.epi_ok = ok0 ? 1u : 0u;
+                sm.epi_ok[g] = ok0 ? 1u : 0u;
             }
-            epilogue_barrier();
-            if (sm.epi_ok == 0u) break;
+            group_barrier(g);
+            if (sm.epi_ok[g] == 0u) break;
             mbar_wait(&sm.acc_full[buf], acc_parity);     // already complete: returns at once, orders this thread
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 
             const float bias_m = bias != nullptr ? bias[m0 + row] : 0.f;
-            const uint32_t lane_base = tmem_base + buf * WN + (static_cast<uint32_t>(warp * 32) << 16);
-#pragma unroll
-            for (int h = 0; h < WN / 128; ++h) {          // 128-column chunk = CB batch items x T steps
-                if (h > 0) {
-                    // the previous chunk's TMA stores must have finished reading the staging tiles
-                    if (threadIdx.x == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
-                    epilogue_barrier();
-                }
-                float u[CB], gate[CB];
-#pragma unroll
-                for (int j = 0; j < CB; ++j) { u[j] = 0.f; gate[j] = 1.f; }
-#pragma unroll
-                for (int t = 0; t < T; ++t) {
-#pragma unroll
-                    for (int c = 0; c < CB; c += 16) {
-                        uint32_t r[16];
-                        tmem_ld16(lane_base + t * BT + h * CB + c, r);
-                        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-                        for (int j = 0; j < 16; ++j) {
-                            const __nv_bfloat16 cur_h =
-                                __float2bfloat16_rn(__fadd_rn(__uint_as_float(r[j]), bias_m));
-                            const float cur = __bfloat162float(cur_h);
-                            const float leak = __fmul_rn(__fmul_rn(alpha, u[c + j]), gate[c + j]);
-                            u[c + j] = __fadd_rn(leak, cur);
-                            const bool s = u[c + j] > thresh;
-                            gate[c + j] = s ? 0.f : 1.f;
-                            const int n = t * CB + c + j;
-                            sm.out_spike[n * BM + row] = __float2bfloat16_rn(s ? 1.f : 0.f);
-                            sm.out_current[n * BM + row] = cur_h;
-                        }
-                    }
-                }
-                if (h == WN / 128 - 1) {
-                    // accumulator drained: hand the TMEM buffer back to the MMA warp
-                    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-                    mbar_arrive(&sm.acc_empty[buf]);
-                }
-                // staging tiles complete: one thread issues the bulk stores
-                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-                epilogue_barrier();
-                if (threadIdx.x == 0) {
-                    tma_store_3d(&map_spike, sm.out_spike, m0, b0 + h * CB, 0);
-                    if (write_current) tma_store_3d(&map_current, sm.out_current, m0, b0 + h * CB, 0);
-                    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
-                }
-            }
+            const uint32_t lane_base = tmem_base + buf * WN + (static_cast<uint32_t>(quarter * 32) << 16);
+            uint64_t* drained_bar = &sm.acc_empty[buf];
+            lif_epilogue_tile<T, WN>(sm.epi[g], staged, g, elected, lane_base, row, bias_m, alpha, thresh, &map_spike,
+                                     &map_current, write_current, m0, b0, [drained_bar] { mbar_arrive(drained_bar); });
         }
-        if (threadIdx.x == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+        // shared memory must outlive the reads of the last stores; the writes themselves complete
+        // before the grid does
+        if (elected) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
     }
 
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -460,6 +526,214 @@ linear_lif_fwd_persistent_kernel(const __grid_constant__ CUtensorMap map_w, cons
     if (warp == 5) {
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
                      "r"(kTmemColsPersistent)
+                     : "memory");
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// CTA-pair variant: a cluster of two CTAs (the two SMs of a TPC) computes a 256 (output neurons)
+// x 256 ((t, b) pairs) tile with tcgen05.mma.cta_group::2. Each CTA stages its own 128 rows of W
+// and HALF of the X tile (time steps [rank*T/2, (rank+1)*T/2) of the tile's 256/T batch items =
+// accumulator columns [rank*128, rank*128+128)); the pair's tensor cores read both halves, so a
+// CTA pulls 32 KB per stage for the flops that cost the single-CTA kernels 48 KB (wide tile) or
+// 64 KB (two narrow tiles) - the quantity that bounds them. Each CTA's tensor memory receives its
+// own 128 neurons x 256 columns, and its epilogue warps run the same LIF epilogue as above.
+//
+// Roles per CTA as before; the MMA issuer runs in the leader (cluster rank 0) only. Both CTAs'
+// TMA loads complete on the LEADER's full barrier (armed with the bytes of both); the leader's
+// tcgen05.commit multicasts the stage-free / accumulator-full arrivals to both CTAs; epilogue
+// threads of both CTAs arrive on the leader's accumulator-empty barrier. One accumulator (256
+// columns), so tiles of one pair are processed back to back without epilogue overlap. No
+// multicast loads. All mbarrier waits are bounded as above; the cluster barriers at entry and
+// exit are reached unconditionally by every thread of both CTAs.
+// ---------------------------------------------------------------------------------------------
+constexpr int PAIR_STAGES = 4;
+constexpr uint32_t kPairTmemCols = 256;
+constexpr int PAIR_N = 256;
+
+struct __align__(1024) PairStorage {
+    __nv_bfloat16 a[PAIR_STAGES][BM * BK];
+    __nv_bfloat16 b[PAIR_STAGES][(PAIR_N / 2) * BK];
+    EpilogueStaging epi[2][2];
+    uint64_t full[PAIR_STAGES];        // used in the leader
+    uint64_t empty[PAIR_STAGES];
+    uint64_t acc_full;
+    uint64_t acc_empty;                // used in the leader: 2 CTAs x 256 epilogue threads arrive
+    uint32_t tmem_base;
+    uint32_t epi_ok[2];
+};
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+// address of the same shared-memory location in the CTA of the given cluster rank
+__device__ __forceinline__ uint32_t mapa_shared(uint32_t addr, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ void tma_load_2d_pair(void* dst, const CUtensorMap* map, uint32_t bar_cluster_addr, int c0,
+                                                 int c1) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(smem_u32(dst)), "l"(map), "r"(bar_cluster_addr), "r"(c0), "r"(c1)
+        : "memory");
+}
+__device__ __forceinline__ void tma_load_3d_pair(void* dst, const CUtensorMap* map, uint32_t bar_cluster_addr, int c0,
+                                                 int c1, int c2) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+        ::"r"(smem_u32(dst)), "l"(map), "r"(bar_cluster_addr), "r"(c0), "r"(c1), "r"(c2)
+        : "memory");
+}
+__device__ __forceinline__ void umma_bf16_pair(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                               uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5, %5, %5, %5, %5}, p;\n\t}"
+        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(0u)
+        : "memory");
+}
+// arrive on the barrier at this shared-memory offset in both CTAs of the pair once the MMAs issued so far retire
+__device__ __forceinline__ void umma_commit_pair(uint64_t* bar) {
+    const uint16_t mask = 3;
+    asm volatile(
+        "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+        ::"r"(smem_u32(bar)), "h"(mask)
+        : "memory");
+}
+
+template <int T>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreadsP, 1)
+linear_lif_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
+                           const __grid_constant__ CUtensorMap map_spike,
+                           const __grid_constant__ CUtensorMap map_current, int write_current,
+                           const float* __restrict__ bias, int B, int K, int M, float alpha, float thresh)
+{
+    constexpr int BT = PAIR_N / T;              // batch items per tile
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
+    PairStorage& sm = *reinterpret_cast<PairStorage*>(
+        (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_ctarank();
+    const bool leader = rank == 0;
+    const int pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
+    const int num_kb = K / BK;
+    const int tiles_m = M / (2 * BM);
+    const int num_tiles = tiles_m * (B / BT);
+
+    if (threadIdx.x == 4 * 32) {
+        for (int s = 0; s < PAIR_STAGES; ++s) { mbar_init(&sm.full[s], 1); mbar_init(&sm.empty[s], 1); }
+        mbar_init(&sm.acc_full, 1);
+        mbar_init(&sm.acc_empty, 512);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_x) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_spike) : "memory");
+    }
+    if (warp == 5) {
+        // one warp of each CTA of the pair takes part in the pair-wide allocation
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sm.tmem_base)),
+                     "r"(kPairTmemCols)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    cluster_sync_all();                         // the peer's barriers are initialised past this point
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = sm.tmem_base;
+
+    if (warp == 4) {
+        // ------------------------------ TMA producer (both CTAs) ------------------
+        if (lane == 0) {
+            int it = 0;
+            bool ok = true;
+            for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
+                const int m0 = (tile % tiles_m) * (2 * BM) + static_cast<int>(rank) * BM;
+                const int b0 = (tile / tiles_m) * BT;
+                for (int kb = 0; kb < num_kb; ++kb, ++it) {
+                    const int s = it % PAIR_STAGES;
+                    const uint32_t parity = ((it / PAIR_STAGES) & 1) ^ 1;
+                    if (!mbar_wait(&sm.empty[s], parity)) { atomicExch(&g_linear_lif_error, 11); ok = false; break; }
+                    const uint32_t full_leader = mapa_shared(smem_u32(&sm.full[s]), 0);
+                    if (leader) mbar_expect_tx(&sm.full[s], 2 * (kStageBytesA + (PAIR_N / 2) * BK * 2));
+                    tma_load_2d_pair(sm.a[s], &map_w, full_leader, kb * BK, m0);
+                    tma_load_3d_pair(sm.b[s], &map_x, full_leader, kb * BK, b0, static_cast<int>(rank) * (T / 2));
+                }
+            }
+        }
+    } else if (warp == 5) {
+        // ------------------------------ MMA issuer (leader CTA only) --------------
+        if (lane == 0 && leader) {
+            constexpr uint32_t idesc = umma_idesc_bf16(2 * BM, PAIR_N);
+            int it = 0, local = 0;
+            bool ok = true;
+            for (int tile = pair; tile < num_tiles && ok; tile += num_pairs, ++local) {
+                if (!mbar_wait(&sm.acc_empty, (local & 1) ^ 1)) { atomicExch(&g_linear_lif_error, 14); break; }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                for (int kb = 0; kb < num_kb; ++kb, ++it) {
+                    const int s = it % PAIR_STAGES;
+                    const uint32_t parity = (it / PAIR_STAGES) & 1;
+                    if (!mbar_wait(&sm.full[s], parity)) { atomicExch(&g_linear_lif_error, 12); ok = false; break; }
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const uint64_t da = umma_desc_sw128(sm.a[s]);
+                    const uint64_t db = umma_desc_sw128(sm.b[s]);
+#pragma unroll
+                    for (int k = 0; k < BK / UMMA_K; ++k)
+                        umma_bf16_pair(tmem_base, da + 2 * k, db + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
+                    umma_commit_pair(&sm.empty[s]);
+                }
+                if (ok) umma_commit_pair(&sm.acc_full);
+            }
+        }
+    } else {
+        // ------------------------------ epilogue groups (both CTAs) ---------------
+        const int g = warp >= 6 ? 1 : 0;
+        const int quarter = warp & 3;
+        const int row = quarter * 32 + lane;
+        const bool elected = lane == 0 && warp == (g ? 6 : 0);
+        const uint32_t acc_empty_leader = mapa_shared(smem_u32(&sm.acc_empty), 0);
+        int local = 0, staged = 0;
+        for (int tile = pair; tile < num_tiles; tile += num_pairs, ++local) {
+            const int m0 = (tile % tiles_m) * (2 * BM) + static_cast<int>(rank) * BM;
+            const int b0 = (tile / tiles_m) * BT;
+            const uint32_t acc_parity = local & 1;
+            if (elected) {
+                const bool ok0 = mbar_wait(&sm.acc_full, acc_parity);
+                if (!ok0) atomicExch(&g_linear_lif_error, 13);
+                sm.epi_ok[g] = ok0 ? 1u : 0u;
+            }
+            group_barrier(g);
+            if (sm.epi_ok[g] == 0u) break;
+            mbar_wait(&sm.acc_full, acc_parity);          // already complete: orders this thread
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+
+            const float bias_m = bias != nullptr ? bias[m0 + row] : 0.f;
+            const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
+            lif_epilogue_tile<T, PAIR_N>(sm.epi[g], staged, g, elected, lane_base, row, bias_m, alpha, thresh, &map_spike,
+                                         &map_current, write_current, m0, b0,
+                                         [acc_empty_leader] { mbar_arrive_cluster(acc_empty_leader); });
+        }
+        if (elected) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+    }
+
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    cluster_sync_all();                         // nobody touches the peer's memory or TMEM past this point
+    if (warp == 5) {
+        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kPairTmemCols)
                      : "memory");
     }
 }
@@ -559,39 +833,62 @@ int launch_persistent(const CUtensorMap& mw, const CUtensorMap& mx, const CUtens
     if (e != cudaSuccess) { snn_internal::set_last_cuda_error(static_cast<int>(e)); return SNN_ERR_CUDA; }
     const int tiles = (M / BM) * (B / (WN / T));
     const int grid = tiles < sms ? tiles : sms;
-    kern<<<grid, kThreads, smem, st>>>(mw, mx, ms, mc, write_current, bias, B, K, M, alpha, thresh);
+    kern<<<grid, kThreadsP, smem, st>>>(mw, mx, ms, mc, write_current, bias, B, K, M, alpha, thresh);
+    e = cudaGetLastError();
+    if (e != cudaSuccess) { snn_internal::set_last_cuda_error(static_cast<int>(e)); return SNN_ERR_CUDA; }
+    return SNN_OK;
+}
+
+template <int T>
+int launch_pair(const CUtensorMap& mw, const CUtensorMap& mx, const CUtensorMap& ms, const CUtensorMap& mc,
+                int write_current, const float* bias, int B, int K, int M, float alpha, float thresh,
+                cudaStream_t st) {
+    static_assert(sizeof(PairStorage) + 1024 <= 227 * 1024, "shared memory budget");
+    const size_t smem = sizeof(PairStorage) + 1024;
+    auto kern = linear_lif_fwd_pair_kernel<T>;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    const int sms = sm_count();
+    if (e == cudaSuccess && sms < 2) e = cudaErrorInvalidDevice;
+    if (e != cudaSuccess) { snn_internal::set_last_cuda_error(static_cast<int>(e)); return SNN_ERR_CUDA; }
+    const int tiles = (M / (2 * BM)) * (B / (PAIR_N / T));
+    const int pairs = tiles < sms / 2 ? tiles : sms / 2;
+    kern<<<2 * pairs, kThreadsP, smem, st>>>(mw, mx, ms, mc, write_current, bias, B, K, M, alpha, thresh);
     e = cudaGetLastError();
     if (e != cudaSuccess) { snn_internal::set_last_cuda_error(static_cast<int>(e)); return SNN_ERR_CUDA; }
     return SNN_OK;
 }
 
 // SNN_LINEAR_LIF_VARIANT: 1 = one-tile-per-CTA kernel (kept for comparison), 2 = persistent kernel
-// with 128-column tiles, 3 = persistent kernel with 256-column tiles where the batch allows;
-// default 0 = persistent kernel, tile width chosen by pick_wide().
+// with 128-column tiles, 3 = persistent kernel with 256-column tiles where the batch allows,
+// 4 = CTA-pair kernel where the shape allows; default 0 = chosen per problem by pick_kernel().
 int variant() {
     static int v = -1;
     if (v < 0) {
         const char* e = getenv("SNN_LINEAR_LIF_VARIANT");
-        v = (e != nullptr && e[0] >= '1' && e[0] <= '3') ? e[0] - '0' : 0;
+        v = (e != nullptr && e[0] >= '1' && e[0] <= '4') ? e[0] - '0' : 0;
     }
     return v;
 }
 
-// A 256-column tile does twice the work of a 128-column one in about 1.5x the time (48 KB
-// instead of 2 x 32 KB through the SM's L2 port), but halves the tile count: compare the rounds
-// of tiles each choice needs on this device.
-bool pick_wide(int T, int B, int M) {
-    if (B % (256 / T) != 0) return false;
+// Which persistent kernel: narrow (128 x 128 tiles), wide (128 x 256) or pair (256 x 256 per CTA
+// pair). Per 128 x 256 of output a CTA pulls 64 KB per K stage as two narrow tiles, 48 KB as a
+// wide tile and 32 KB in a pair, and that traffic is what bounds the mainloop; the wider shapes
+// halve the tile count, so compare the rounds of tiles each choice needs on this device.
+enum Kernel { kNarrow = 0, kWide = 1, kPair = 2 };
+Kernel pick_kernel(int T, int B, int M) {
+    const bool wide_ok = B % (256 / T) == 0;
+    const bool pair_ok = wide_ok && M % (2 * BM) == 0;
     const int v = variant();
-    if (v == 2) return false;
-    if (v == 3) return true;
+    if (v == 2 || !wide_ok) return kNarrow;
+    if (v == 3) return kWide;
+    if (v == 4) return pair_ok ? kPair : kWide;
     const int sms = sm_count();
-    if (sms <= 0) return false;
+    if (sms <= 0) return kNarrow;
     const long long t128 = static_cast<long long>(M / BM) * (B / (128 / T));
     const long long t256 = t128 / 2;
-    const long long cost128 = 2 * ((t128 + sms - 1) / sms);
-    const long long cost256 = 3 * ((t256 + sms - 1) / sms);
-    return cost256 < cost128;
+    const long long cost128 = 4 * ((t128 + sms - 1) / sms);
+    const long long cost256 = 6 * ((t256 + sms - 1) / sms);
+    return cost256 < cost128 ? kWide : kNarrow;
 }
 
 }  // namespace
@@ -618,15 +915,17 @@ int snn_linear_lif_fwd(const void* x, const void* weight, const float* bias, voi
     if (!al(x, 16) || !al(weight, 16) || !al(spike, 2) || !al(current, 2) || !al(bias, 4)) return SNN_ERR_ALIGN;
 
     const bool one_tile = variant() == 1 || !al(spike, 16) || !al(current, 16);
-    const bool wide = !one_tile && pick_wide(static_cast<int>(T), static_cast<int>(B), static_cast<int>(M));
-    const cuuint32_t tile_n = wide ? 256 : 128;
+    const Kernel kernel = one_tile ? kNarrow : pick_kernel(static_cast<int>(T), static_cast<int>(B), static_cast<int>(M));
+    const cuuint32_t tile_n = kernel == kNarrow ? 128 : 256;
+    // a pair member fetches half of the tile's time steps
+    const cuuint32_t tile_t = static_cast<cuuint32_t>(kernel == kPair ? T / 2 : T);
     CUtensorMap mw, mx;
     const cuuint64_t wdims[2] = {static_cast<cuuint64_t>(K), static_cast<cuuint64_t>(M)};
     const cuuint64_t wstr[1] = {static_cast<cuuint64_t>(K) * 2};
     const cuuint32_t wbox[2] = {BK, BM};
     const cuuint64_t xdims[3] = {static_cast<cuuint64_t>(K), static_cast<cuuint64_t>(B), static_cast<cuuint64_t>(T)};
     const cuuint64_t xstr[2] = {static_cast<cuuint64_t>(K) * 2, static_cast<cuuint64_t>(B) * K * 2};
-    const cuuint32_t xbox[3] = {BK, tile_n / static_cast<cuuint32_t>(T), static_cast<cuuint32_t>(T)};
+    const cuuint32_t xbox[3] = {BK, tile_n / static_cast<cuuint32_t>(T), tile_t};
     if (!cached_map(&mw, weight, 2, wdims, wstr, wbox) || !cached_map(&mx, x, 3, xdims, xstr, xbox)) {
         snn_internal::set_last_cuda_error(static_cast<int>(cudaErrorInvalidValue));
         return SNN_ERR_CUDA;
@@ -640,7 +939,7 @@ int snn_linear_lif_fwd(const void* x, const void* weight, const float* bias, voi
     CUtensorMap ms, mc;
     const cuuint64_t odims[3] = {static_cast<cuuint64_t>(M), static_cast<cuuint64_t>(B), static_cast<cuuint64_t>(T)};
     const cuuint64_t ostr[2] = {static_cast<cuuint64_t>(M) * 2, static_cast<cuuint64_t>(B) * M * 2};
-    const cuuint32_t obox[3] = {BM, static_cast<cuuint32_t>(BN / T), static_cast<cuuint32_t>(T)};
+    const cuuint32_t obox[3] = {BM, static_cast<cuuint32_t>(32 / T), static_cast<cuuint32_t>(T)};   // one epilogue unit
     if (!cached_map(&ms, spike, 3, odims, ostr, obox, false) ||
         (current != nullptr && !cached_map(&mc, current, 3, odims, ostr, obox, false))) {
         snn_internal::set_last_cuda_error(static_cast<int>(cudaErrorInvalidValue));
@@ -648,7 +947,11 @@ int snn_linear_lif_fwd(const void* x, const void* weight, const float* bias, voi
     }
     if (current == nullptr) mc = ms;
     const int wc = current != nullptr ? 1 : 0;
-    if (wide) {
+    if (kernel == kPair) {
+        if (T == 4) return launch_pair<4>(mw, mx, ms, mc, wc, bias, Bi, Ki, Mi, alpha, thresh, st);
+        return launch_pair<8>(mw, mx, ms, mc, wc, bias, Bi, Ki, Mi, alpha, thresh, st);
+    }
+    if (kernel == kWide) {
         if (T == 4) return launch_persistent<4, 256>(mw, mx, ms, mc, wc, bias, Bi, Ki, Mi, alpha, thresh, st);
         return launch_persistent<8, 256>(mw, mx, ms, mc, wc, bias, Bi, Ki, Mi, alpha, thresh, st);
     }

@@ -67,11 +67,11 @@ def test_fused_forward_against_reference_gemm_and_oracle(capi, shape):
     assert capi.linear_lif_error() == 0
 
 
-@pytest.mark.parametrize("variant", ["1", "2", "3"])
+@pytest.mark.parametrize("variant", ["1", "2", "3", "4"])
 def test_each_kernel_variant_passes_the_forward_checks(capi, variant):
     """The library picks a kernel per problem; the environment switch forces the one-tile kernel (1),
-    128-column persistent tiles (2) or 256-column persistent tiles wherever the batch allows (3). It
-    is read once per process, so each forced variant runs the forward test in a child process."""
+    128-column persistent tiles (2), 256-column persistent tiles wherever the batch allows (3) or the
+    CTA-pair kernel wherever the shape allows (4). It is read once per process, so each forced variant runs the forward test in a child process."""
     if os.environ.get("SNN_LINEAR_LIF_VARIANT"):
         pytest.skip("already inside a forced-variant run")
     env = dict(os.environ, SNN_LINEAR_LIF_VARIANT=variant)
