@@ -70,8 +70,20 @@ def build_tuner(cache_policy=None) -> str:
     return out
 
 
+def build_trace() -> str:
+    """Build csrc/tune/linear_lif_trace (phase timeline of the fused linear + LIF kernels; needs a GPU to run)."""
+    out = os.path.join(CSRC, "tune", "linear_lif_trace")
+    nvcc = os.environ.get("NVCC", "nvcc")
+    cmd = [nvcc, "-O3", "-std=c++17", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo",
+           "-diag-suppress", "177"]
+    subprocess.run(cmd + ["-o", out, os.path.join(CSRC, "tune", "linear_lif_trace.cu")], check=True)
+    return out
+
+
 if __name__ == "__main__":
-    if "--tuner" in sys.argv:
+    if "--trace" in sys.argv:
+        print(build_trace())
+    elif "--tuner" in sys.argv:
         pol = sys.argv[sys.argv.index("--cache-policy") + 1] if "--cache-policy" in sys.argv else None
         print(build_tuner(pol))
     else:

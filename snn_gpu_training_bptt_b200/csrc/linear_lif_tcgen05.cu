@@ -55,6 +55,19 @@ constexpr long long kWaitCycles = 2000000000LL;       // ~1 s
 
 __device__ int g_linear_lif_error = 0;
 
+// Phase stamps for csrc/tune/linear_lif_trace.cu (built with -DSNN_LINEAR_LIF_TRACE): slot <- the
+// SM's cycle counter, one row per CTA. Compiled out of the library.
+#ifdef SNN_LINEAR_LIF_TRACE
+constexpr int kTraceSlots = 64;
+__device__ long long g_linear_lif_trace[1024][kTraceSlots];
+#define SNN_TRACE(slot) do { if (blockIdx.x < 1024) g_linear_lif_trace[blockIdx.x][slot] = clock64(); } while (0)
+#else
+#define SNN_TRACE(slot) do { } while (0)
+#endif
+// slots: 0..39 = operands of K stage i of the CTA's first tile seen by the MMA issuer, 40 = accumulator of
+// the first tile committed, 42 / 52 = epilogue group 0 / 1 sees the first accumulator, 43 / 53 = group has
+// issued its last store, 44 / 54 = that store has been read out, 45 = kernel entry, 46 = set-up done
+
 struct __align__(1024) SharedStorage {
     __nv_bfloat16 a[STAGES][BM * BK];
     __nv_bfloat16 b[STAGES][BN * BK];
@@ -264,11 +277,10 @@ linear_lif_fwd_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
 // fill the other one; the epilogue writes its bf16 currents / spikes into a shared-memory tile
 // laid out [t][b][m] and hands it to one 3-D TMA store per output instead of 2-byte stores.
 //
-// WN = accumulator columns per tile, 128 or 256. The mainloop is bound by what one SM can pull
-// from L2 (measured ~58 B/clk against 128 B/clk needed to feed 128x128x64 MMAs at full rate);
-// a 128 x 256 tile moves 48 KB per stage for twice the flops of a 128 x 128 tile's 32 KB, so
-// the wide tile is used when it does not cost a wave of parallelism (see pick_wide()). The
-// epilogue handles a wide tile as two 128-column chunks through the same staging buffers.
+// WN = accumulator columns per tile, 128 or 256. Measured with linear_lif_trace: a K stage (four
+// tcgen05.mma 128 x WN x 16) takes ~535 cycles for WN = 256, i.e. ~95 % of the tensor pipe's
+// rate, and the same ~531 cycles for WN = 128 - half the flops. So the wide tile is used
+// whenever it does not cost a round of parallelism (see pick_kernel()).
 // ---------------------------------------------------------------------------------------------
 // Threads of the persistent and pair kernels: warps 0-3 = epilogue group 0, warp 4 = TMA producer,
 // warp 5 = MMA issuer / TMEM owner, warps 6-9 = epilogue group 1. A warp may only touch the TMEM
@@ -422,6 +434,7 @@ linear_lif_fwd_persistent_kernel(const __grid_constant__ CUtensorMap map_w, cons
         (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) SNN_TRACE(45);
     const int num_kb = K / BK;
     const int tiles_m = M / BM;
     const int num_tiles = tiles_m * (B / BT);
@@ -444,6 +457,7 @@ linear_lif_fwd_persistent_kernel(const __grid_constant__ CUtensorMap map_w, cons
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = sm.tmem_base;
+    if (threadIdx.x == 0) SNN_TRACE(46);
 
     if (warp == 4) {
         // ------------------------------ TMA producer ------------------------------
@@ -479,6 +493,7 @@ linear_lif_fwd_persistent_kernel(const __grid_constant__ CUtensorMap map_w, cons
                     const uint32_t parity = (it / PSTAGES) & 1;
                     if (!mbar_wait(&sm.full[s], parity)) { atomicExch(&g_linear_lif_error, 2); ok = false; break; }
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    if (it < 40) SNN_TRACE(it);
                     const uint64_t da = umma_desc_sw128(sm.a[s]);
                     const uint64_t db = umma_desc_sw128(sm.b[s]);
 #pragma unroll
@@ -487,6 +502,7 @@ linear_lif_fwd_persistent_kernel(const __grid_constant__ CUtensorMap map_w, cons
                     umma_commit(&sm.empty[s]);
                 }
                 if (ok) umma_commit(&sm.acc_full[buf]);
+                if (local == 0) SNN_TRACE(40);
             }
         }
     } else {
@@ -506,6 +522,7 @@ linear_lif_fwd_persistent_kernel(const __grid_constant__ CUtensorMap map_w, cons
                 sm.epi_ok[g] = ok0 ? 1u : 0u;
             }
             group_barrier(g);
+            if (elected && local == 0) SNN_TRACE(42 + 10 * g);
             if (sm.epi_ok[g] == 0u) break;
             mbar_wait(&sm.acc_full[buf], acc_parity);     // already complete: returns at once, orders this thread
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -518,7 +535,9 @@ linear_lif_fwd_persistent_kernel(const __grid_constant__ CUtensorMap map_w, cons
         }
         // shared memory must outlive the reads of the last stores; the writes themselves complete
         // before the grid does
+        if (elected) SNN_TRACE(43 + 10 * g);
         if (elected) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+        if (elected) SNN_TRACE(44 + 10 * g);
     }
 
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -536,8 +555,10 @@ linear_lif_fwd_persistent_kernel(const __grid_constant__ CUtensorMap map_w, cons
 // and HALF of the X tile (time steps [rank*T/2, (rank+1)*T/2) of the tile's 256/T batch items =
 // accumulator columns [rank*128, rank*128+128)); the pair's tensor cores read both halves, so a
 // CTA pulls 32 KB per stage for the flops that cost the single-CTA kernels 48 KB (wide tile) or
-// 64 KB (two narrow tiles) - the quantity that bounds them. Each CTA's tensor memory receives its
-// own 128 neurons x 256 columns, and its epilogue warps run the same LIF epilogue as above.
+// 64 KB (two narrow tiles). Each CTA's tensor memory receives its own 128 neurons x 256 columns,
+// and its epilogue warps run the same LIF epilogue as above. The wide-tile mainloop is already
+// tensor-bound, so at the sizes measured the pair kernel is no faster (K stage 547 cycles, plus
+// ~1000 cycles of cluster set-up); it is selected only by SNN_LINEAR_LIF_VARIANT=4.
 //
 // Roles per CTA as before; the MMA issuer runs in the leader (cluster rank 0) only. Both CTAs'
 // TMA loads complete on the LEADER's full barrier (armed with the bytes of both); the leader's
@@ -626,6 +647,7 @@ linear_lif_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
         (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) SNN_TRACE(45);
     const uint32_t rank = cluster_ctarank();
     const bool leader = rank == 0;
     const int pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
@@ -654,6 +676,7 @@ linear_lif_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
     cluster_sync_all();                         // the peer's barriers are initialised past this point
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = sm.tmem_base;
+    if (threadIdx.x == 0) SNN_TRACE(46);
 
     if (warp == 4) {
         // ------------------------------ TMA producer (both CTAs) ------------------
@@ -688,6 +711,7 @@ linear_lif_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
                     const uint32_t parity = (it / PAIR_STAGES) & 1;
                     if (!mbar_wait(&sm.full[s], parity)) { atomicExch(&g_linear_lif_error, 12); ok = false; break; }
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    if (it < 40) SNN_TRACE(it);
                     const uint64_t da = umma_desc_sw128(sm.a[s]);
                     const uint64_t db = umma_desc_sw128(sm.b[s]);
 #pragma unroll
@@ -696,6 +720,7 @@ linear_lif_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
                     umma_commit_pair(&sm.empty[s]);
                 }
                 if (ok) umma_commit_pair(&sm.acc_full);
+                if (local == 0) SNN_TRACE(40);
             }
         }
     } else {
@@ -716,6 +741,7 @@ linear_lif_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
                 sm.epi_ok[g] = ok0 ? 1u : 0u;
             }
             group_barrier(g);
+            if (elected && local == 0) SNN_TRACE(42 + 10 * g);
             if (sm.epi_ok[g] == 0u) break;
             mbar_wait(&sm.acc_full, acc_parity);          // already complete: orders this thread
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -726,7 +752,9 @@ linear_lif_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
                                          &map_current, write_current, m0, b0,
                                          [acc_empty_leader] { mbar_arrive_cluster(acc_empty_leader); });
         }
+        if (elected) SNN_TRACE(43 + 10 * g);
         if (elected) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+        if (elected) SNN_TRACE(44 + 10 * g);
     }
 
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -871,9 +899,8 @@ int variant() {
 }
 
 // Which persistent kernel: narrow (128 x 128 tiles), wide (128 x 256) or pair (256 x 256 per CTA
-// pair). Per 128 x 256 of output a CTA pulls 64 KB per K stage as two narrow tiles, 48 KB as a
-// wide tile and 32 KB in a pair, and that traffic is what bounds the mainloop; the wider shapes
-// halve the tile count, so compare the rounds of tiles each choice needs on this device.
+// pair, on request only). A wide tile costs about as much mainloop time as ONE narrow tile but
+// halves the tile count, so compare the rounds of tiles each choice needs on this device.
 enum Kernel { kNarrow = 0, kWide = 1, kPair = 2 };
 Kernel pick_kernel(int T, int B, int M) {
     const bool wide_ok = B % (256 / T) == 0;
@@ -886,9 +913,9 @@ Kernel pick_kernel(int T, int B, int M) {
     if (sms <= 0) return kNarrow;
     const long long t128 = static_cast<long long>(M / BM) * (B / (128 / T));
     const long long t256 = t128 / 2;
-    const long long cost128 = 4 * ((t128 + sms - 1) / sms);
-    const long long cost256 = 6 * ((t256 + sms - 1) / sms);
-    return cost256 < cost128 ? kWide : kNarrow;
+    const long long rounds128 = (t128 + sms - 1) / sms;
+    const long long rounds256 = (t256 + sms - 1) / sms;
+    return 10 * rounds256 < 9 * rounds128 ? kWide : kNarrow;     // a wide round costs ~1.1 narrow rounds
 }
 
 }  // namespace
@@ -958,6 +985,15 @@ int snn_linear_lif_fwd(const void* x, const void* weight, const float* bias, voi
     if (T == 4) return launch_persistent<4, 128>(mw, mx, ms, mc, wc, bias, Bi, Ki, Mi, alpha, thresh, st);
     return launch_persistent<8, 128>(mw, mx, ms, mc, wc, bias, Bi, Ki, Mi, alpha, thresh, st);
 }
+
+#ifdef SNN_LINEAR_LIF_TRACE
+// trace builds only: copies the stamps of the first `ctas` CTAs (kTraceSlots values each) to `out`
+int snn_linear_lif_trace_read(long long* out, int ctas) {
+    if (ctas < 0 || ctas > 1024) return SNN_ERR_SHAPE;
+    cudaError_t e = cudaMemcpyFromSymbol(out, g_linear_lif_trace, sizeof(long long) * kTraceSlots * ctas);
+    return e == cudaSuccess ? SNN_OK : SNN_ERR_CUDA;
+}
+#endif
 
 int snn_linear_lif_error(int reset) {
     int v = 0;
