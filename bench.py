@@ -295,11 +295,17 @@ def run_ours(args):
             dist.all_reduce(tt, op=dist.ReduceOp.MAX)
             dt = float(tt.item())
         same = bool(torch.equal(hs[:, :4096].to(dev), spike.view(T, N)[:, :4096]))
+        copy_ms = _host_link_copy_ms(hx, hg, hs, hgx, dev)
         e2e = {"value": round(gbps(n_e2e * world, dt), 2), "unit": "GB/s",
                "h2d_bytes_per_step": pipe.h2d_bytes, "d2h_bytes_per_step": pipe.d2h_bytes,
                "ms_per_step": round(dt * 1e3, 3), "neurons_per_gpu": n_e2e,
                "launches_per_step": pipe.launches_per_run, "matches_device_run": same,
-               "how": "pinned host x,grad -> 3-stream chunked H2D / snn_lif_fwd / snn_lif_bwd / D2H of spike,grad_x"}
+               "how": "pinned host x,grad -> 3-stream chunked H2D / snn_lif_fwd / snn_lif_bwd / D2H of spike,grad_x",
+               "host_link": {"copy_only_ms": round(copy_ms, 3),
+                             "gbs_each_way": round(pipe.h2d_bytes / copy_ms / 1e6, 2),
+                             "frac": round(copy_ms / (dt * 1e3), 4),
+                             "what": "the same bytes copied H2D and D2H at once with no kernels (rank 0's "
+                                     "link); frac = that time / the end-to-end step"}}
         del hx, hg, hs, hgx, pipe
         break
 
@@ -376,6 +382,34 @@ def _time_kernel(fn, reps, flush=None):
         e1.synchronize()
         times.append(e0.elapsed_time(e1))
     return statistics.median(times)
+
+
+def _host_link_copy_ms(hx, hg, hs, hgx, dev, reps=2):
+    """Time of moving one end-to-end step's bytes over the host link and nothing else: the pinned
+    inputs H2D on one stream while as many bytes go D2H into the pinned outputs on another."""
+    import torch
+    T, n = hx.shape
+    chunk = min(n, 1 << 22)
+    up, down = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
+    stage_in = torch.empty((2, T, chunk), dtype=hx.dtype, device=dev)
+    stage_out = torch.zeros((2, T, chunk), dtype=hx.dtype, device=dev)
+    torch.cuda.synchronize(dev)
+    best = float("inf")
+    for _ in range(reps + 1):                                   # first pass warms up
+        t0 = time.perf_counter()
+        for lo in range(0, n, chunk):
+            m = min(chunk, n - lo)
+            with torch.cuda.stream(up):                         # contiguous rows, as the pipeline copies them
+                for t in range(T):
+                    stage_in[0, t, :m].copy_(hx[t, lo:lo + m], non_blocking=True)
+                    stage_in[1, t, :m].copy_(hg[t, lo:lo + m], non_blocking=True)
+            with torch.cuda.stream(down):
+                for t in range(T):
+                    hs[t, lo:lo + m].copy_(stage_out[0, t, :m], non_blocking=True)
+                    hgx[t, lo:lo + m].copy_(stage_out[1, t, :m], non_blocking=True)
+        torch.cuda.synchronize(dev)
+        best = min(best, (time.perf_counter() - t0) * 1e3)
+    return best
 
 
 def _time_graphed(fn, reps=20, per_graph=10):
