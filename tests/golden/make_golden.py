@@ -2,7 +2,7 @@
 
 Run once, in a container where the reference checkout is mounted:
 
-    python tests/golden/make_golden.py [--ref /path/to/reference]
+    python tests/golden/make_golden.py --ref /path/to/reference
 
 It imports ``snnlib/example/gold_op.py`` of liangling76/snn_gpu_training_bptt (pure PyTorch,
 CPU) and records, for seeded inputs, the membrane potentials, spikes and input gradients
@@ -173,7 +173,7 @@ def record_reference_model_layouts(ref_root):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--ref", default="/root/reference")
+    ap.add_argument("--ref", required=True, help="checkout of liangling76/snn_gpu_training_bptt")
     args = ap.parse_args()
     sys.path.insert(0, os.path.join(args.ref, "snnlib", "example"))
     import gold_op as gop  # the reference's module
