@@ -356,10 +356,22 @@ def run_ours(args):
         }
         if world == 1 and not args.no_cpu:
             out["cpu_baseline"] = cpu_baseline_block()
+            if trainer is not None:
+                trainer["cpu_baseline"] = cpu_trainer_block()
         print(json.dumps(out))
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
+
+
+def cpu_trainer_block():
+    """The trainer's network as a plain-PyTorch CPU restatement around the oracle's LIF, a few SGD
+    steps at batch 8 on all host cores (the only CPU-runnable form of the reference's training)."""
+    from oracle import cpu_trainer
+    r = cpu_trainer.time_training(batch=8, steps=2, warmup=1, time_steps=8)
+    return {"value": round(r["samples_per_s"], 2), "unit": "samples/s", "cores": r["cores"], "kind": "port",
+            "sample": "same VGG-style network, T=8, plain PyTorch ops + autograd port of the reference's "
+                      "gold_fire, fp32, batch 8, %d SGD steps, %.0f ms/step" % (r["steps"], r["ms_per_step"])}
 
 
 # ----------------------------------------------------------------------------------------------

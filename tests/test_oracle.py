@@ -115,3 +115,26 @@ def test_config1_digest(config1_digest):
     assert abs(float(s.mean(dtype=np.float64)) - float(d["spike_rate"])) < 1e-12
     stride = int(d["stride"])
     assert np.array_equal(gx.reshape(-1)[::stride], d["gx_sample"])
+
+
+def test_cpu_trainer_restatement_steps_and_learns():
+    """The CPU restatement of the benchmark network (bench.py's trainer baseline): a narrow copy takes
+    SGD steps on one fixed batch, every parameter receives a finite gradient and the loss goes down."""
+    from oracle import cpu_trainer
+    torch.manual_seed(0)
+    net = cpu_trainer.GoldSpikingVGG(time_steps=4, widths=(4, 8, 8), image=16, hidden=16)
+    images, labels = torch.rand(6, 3, 16, 16), torch.tensor([0, 1, 2, 3, 4, 5])
+    opt = torch.optim.SGD(net.parameters(), lr=0.05, momentum=0.9)
+    losses = []
+    for _ in range(12):
+        opt.zero_grad()
+        loss = torch.nn.functional.cross_entropy(net(images), labels)
+        loss.backward()
+        for name, p in net.named_parameters():
+            assert p.grad is not None and bool(torch.isfinite(p.grad).all()), name
+        opt.step()
+        losses.append(float(loss))
+    assert min(losses[-3:]) < losses[0]
+    r = cpu_trainer.time_training(batch=2, steps=1, warmup=0, time_steps=2, threads=2, widths=(4, 8, 8),
+                                  image=16, hidden=16)
+    assert r["samples_per_s"] > 0 and r["cores"] == 2 and np.isfinite(r["final_loss"])
