@@ -439,12 +439,22 @@ linear_lif_fwd_persistent_kernel(const __grid_constant__ CUtensorMap map_w, cons
     const int tiles_m = M / BM;
     const int num_tiles = tiles_m * (B / BT);
 
+    int preloaded = 0;                          // K stages the producer thread has already requested
     if (threadIdx.x == 4 * 32) {
         for (int s = 0; s < PSTAGES; ++s) { mbar_init(&sm.full[s], 1); mbar_init(&sm.empty[s], 1); }
         for (int i = 0; i < 2; ++i) { mbar_init(&sm.acc_full[i], 1); mbar_init(&sm.acc_empty[i], 256); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
-        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_x) : "memory");
+        // The first stages of the first tile need nothing but these barriers: request them now so
+        // the TMEM allocation and the block-wide sync below overlap the first loads' latency.
+        if (blockIdx.x < num_tiles) {
+            const int m0 = (blockIdx.x % tiles_m) * BM, b0 = (blockIdx.x / tiles_m) * BT;
+            preloaded = num_kb < PSTAGES ? num_kb : PSTAGES;
+            for (int kb = 0; kb < preloaded; ++kb) {
+                mbar_expect_tx(&sm.full[kb], kStageBytesA + PersistentCfg<WN>::kStageBytesB);
+                tma_load_2d(sm.a[kb], &map_w, &sm.full[kb], kb * BK, m0);
+                tma_load_3d(sm.b[kb], &map_x, &sm.full[kb], kb * BK, b0, 0);
+            }
+        }
         asm volatile("prefetch.tensormap [%0];" ::"l"(&map_spike) : "memory");
     }
     if (warp == 5) {
@@ -467,6 +477,7 @@ linear_lif_fwd_persistent_kernel(const __grid_constant__ CUtensorMap map_w, cons
             for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
                 const int m0 = (tile % tiles_m) * BM, b0 = (tile / tiles_m) * BT;
                 for (int kb = 0; kb < num_kb; ++kb, ++it) {
+                    if (it < preloaded) continue;             // requested before the set-up sync
                     const int s = it % PSTAGES;
                     const uint32_t parity = ((it / PSTAGES) & 1) ^ 1;
                     if (!mbar_wait(&sm.empty[s], parity)) { atomicExch(&g_linear_lif_error, 1); ok = false; break; }
