@@ -542,7 +542,7 @@ def run_linear_lif(args):
     from snn_gpu_training_bptt_b200 import _capi, snnlib, snnlib_func as sf
     dev = torch.device("cuda", 0)
     torch.cuda.set_device(dev)
-    T, B, K, M = 8, 256, 2048, 2048
+    T, B, K, M = 8, args.batch, 2048, 2048       # --batch 256 = the reference-sized layer
     torch.manual_seed(1234)
     lin = torch.nn.Linear(K, M).to(dev)
     fwd_flops, all_flops = 2.0 * T * B * K * M, 2.0 * T * B * K * M * 3
@@ -558,7 +558,7 @@ def run_linear_lif(args):
         tf = flops / ms / 1e9
         print(json.dumps({"metric": name, "value": round(tf, 1), "unit": "TFLOP/s", "dtype": dtype,
                           "ms": round(ms, 4), "frac_of_bf16_burst_peak": round(tf / peak_tf, 4),
-                          "config": {"workload": "fc 2048->2048 + LIF, T=8, batch 256", "path": path}}))
+                          "config": {"workload": "fc 2048->2048 + LIF, T=8, batch %d" % B, "path": path}}))
 
     xb = (torch.rand((T, B, K), device=dev) < 0.2).to(torch.bfloat16)
     wb = lin.weight.detach().to(torch.bfloat16)
@@ -593,6 +593,7 @@ def main():
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg")
+    ap.add_argument("--batch", type=int, default=256, help="batch size of --workload linear_lif (a multiple of 32)")
     ap.add_argument("--no-trainer", action="store_true", help="skip the spiking-CNN training leg")
     ap.add_argument("--trainer-steps", type=int, default=30)
     ap.add_argument("--log2n", type=int, default=26,

@@ -567,20 +567,22 @@ linear_lif_fwd_persistent_kernel(const __grid_constant__ CUtensorMap map_w, cons
 // accumulator columns [rank*128, rank*128+128)); the pair's tensor cores read both halves, so a
 // CTA pulls 32 KB per stage for the flops that cost the single-CTA kernels 48 KB (wide tile) or
 // 64 KB (two narrow tiles). Each CTA's tensor memory receives its own 128 neurons x 256 columns,
-// and its epilogue warps run the same LIF epilogue as above. The wide-tile mainloop is already
-// tensor-bound, so at the sizes measured the pair kernel is no faster (K stage 547 cycles, plus
-// ~1000 cycles of cluster set-up); it is selected only by SNN_LINEAR_LIF_VARIANT=4.
+// and its epilogue warps run the same LIF epilogue as above. While the operands fit in L2 and
+// neighbouring CTAs run in step (config-3 size) the wide-tile mainloop is already tensor-bound
+// and the pair kernel is no faster (K stage 547 cycles, plus ~1000 cycles of cluster set-up);
+// with many tiles per CTA the wide kernel's stages stretch to 900-1300 cycles waiting for
+// operands, and the pair's lower traffic pays: see pick_kernel().
 //
 // Roles per CTA as before; the MMA issuer runs in the leader (cluster rank 0) only. Both CTAs'
 // TMA loads complete on the LEADER's full barrier (armed with the bytes of both); the leader's
 // tcgen05.commit multicasts the stage-free / accumulator-full arrivals to both CTAs; epilogue
-// threads of both CTAs arrive on the leader's accumulator-empty barrier. One accumulator (256
-// columns), so tiles of one pair are processed back to back without epilogue overlap. No
-// multicast loads. All mbarrier waits are bounded as above; the cluster barriers at entry and
+// threads of both CTAs arrive on the leader's accumulator-empty barriers. Two accumulators
+// (2 x 256 columns = all of tensor memory), so the epilogue of one tile overlaps the MMAs of the
+// pair's next tile. No multicast loads. All mbarrier waits are bounded as above; the cluster barriers at entry and
 // exit are reached unconditionally by every thread of both CTAs.
 // ---------------------------------------------------------------------------------------------
 constexpr int PAIR_STAGES = 4;
-constexpr uint32_t kPairTmemCols = 256;
+constexpr uint32_t kPairTmemCols = 512;      // two accumulators of 256 columns: all of tensor memory
 constexpr int PAIR_N = 256;
 
 struct __align__(1024) PairStorage {
@@ -589,8 +591,8 @@ struct __align__(1024) PairStorage {
     EpilogueStaging epi[2][2];
     uint64_t full[PAIR_STAGES];        // used in the leader
     uint64_t empty[PAIR_STAGES];
-    uint64_t acc_full;
-    uint64_t acc_empty;                // used in the leader: 2 CTAs x 256 epilogue threads arrive
+    uint64_t acc_full[2];
+    uint64_t acc_empty[2];             // used in the leader: 2 CTAs x 256 epilogue threads arrive
     uint32_t tmem_base;
     uint32_t epi_ok[2];
 };
@@ -668,8 +670,7 @@ linear_lif_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
 
     if (threadIdx.x == 4 * 32) {
         for (int s = 0; s < PAIR_STAGES; ++s) { mbar_init(&sm.full[s], 1); mbar_init(&sm.empty[s], 1); }
-        mbar_init(&sm.acc_full, 1);
-        mbar_init(&sm.acc_empty, 512);
+        for (int i = 0; i < 2; ++i) { mbar_init(&sm.acc_full[i], 1); mbar_init(&sm.acc_empty[i], 512); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(&map_x) : "memory");
@@ -715,8 +716,11 @@ linear_lif_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
             int it = 0, local = 0;
             bool ok = true;
             for (int tile = pair; tile < num_tiles && ok; tile += num_pairs, ++local) {
-                if (!mbar_wait(&sm.acc_empty, (local & 1) ^ 1)) { atomicExch(&g_linear_lif_error, 14); break; }
+                const int buf = local & 1;
+                const uint32_t acc_parity = ((local >> 1) & 1) ^ 1;      // first use of a buffer passes
+                if (!mbar_wait(&sm.acc_empty[buf], acc_parity)) { atomicExch(&g_linear_lif_error, 14); break; }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t tmem_acc = tmem_base + buf * PAIR_N;
                 for (int kb = 0; kb < num_kb; ++kb, ++it) {
                     const int s = it % PAIR_STAGES;
                     const uint32_t parity = (it / PAIR_STAGES) & 1;
@@ -727,10 +731,10 @@ linear_lif_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
                     const uint64_t db = umma_desc_sw128(sm.b[s]);
 #pragma unroll
                     for (int k = 0; k < BK / UMMA_K; ++k)
-                        umma_bf16_pair(tmem_base, da + 2 * k, db + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
+                        umma_bf16_pair(tmem_acc, da + 2 * k, db + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
                     umma_commit_pair(&sm.empty[s]);
                 }
-                if (ok) umma_commit_pair(&sm.acc_full);
+                if (ok) umma_commit_pair(&sm.acc_full[buf]);
                 if (local == 0) SNN_TRACE(40);
             }
         }
@@ -740,25 +744,28 @@ linear_lif_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
         const int quarter = warp & 3;
         const int row = quarter * 32 + lane;
         const bool elected = lane == 0 && warp == (g ? 6 : 0);
-        const uint32_t acc_empty_leader = mapa_shared(smem_u32(&sm.acc_empty), 0);
+        const uint32_t acc_empty_leader0 = mapa_shared(smem_u32(&sm.acc_empty[0]), 0);
+        const uint32_t acc_empty_leader1 = mapa_shared(smem_u32(&sm.acc_empty[1]), 0);
         int local = 0, staged = 0;
         for (int tile = pair; tile < num_tiles; tile += num_pairs, ++local) {
             const int m0 = (tile % tiles_m) * (2 * BM) + static_cast<int>(rank) * BM;
             const int b0 = (tile / tiles_m) * BT;
-            const uint32_t acc_parity = local & 1;
+            const int buf = local & 1;
+            const uint32_t acc_parity = (local >> 1) & 1;
             if (elected) {
-                const bool ok0 = mbar_wait(&sm.acc_full, acc_parity);
+                const bool ok0 = mbar_wait(&sm.acc_full[buf], acc_parity);
                 if (!ok0) atomicExch(&g_linear_lif_error, 13);
                 sm.epi_ok[g] = ok0 ? 1u : 0u;
             }
             group_barrier(g);
             if (elected && local == 0) SNN_TRACE(42 + 10 * g);
             if (sm.epi_ok[g] == 0u) break;
-            mbar_wait(&sm.acc_full, acc_parity);          // already complete: orders this thread
+            mbar_wait(&sm.acc_full[buf], acc_parity);     // already complete: orders this thread
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 
             const float bias_m = bias != nullptr ? bias[m0 + row] : 0.f;
-            const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
+            const uint32_t lane_base = tmem_base + buf * PAIR_N + (static_cast<uint32_t>(quarter * 32) << 16);
+            const uint32_t acc_empty_leader = buf ? acc_empty_leader1 : acc_empty_leader0;
             lif_epilogue_tile<T, PAIR_N>(sm.epi[g], staged, g, elected, lane_base, row, bias_m, alpha, thresh, &map_spike,
                                          &map_current, write_current, m0, b0,
                                          [acc_empty_leader] { mbar_arrive_cluster(acc_empty_leader); });
@@ -910,8 +917,10 @@ int variant() {
 }
 
 // Which persistent kernel: narrow (128 x 128 tiles), wide (128 x 256) or pair (256 x 256 per CTA
-// pair, on request only). A wide tile costs about as much mainloop time as ONE narrow tile but
-// halves the tile count, so compare the rounds of tiles each choice needs on this device.
+// pair). A wide tile costs about as much mainloop time as ONE narrow tile but halves the tile
+// count, so compare the rounds of tiles each choice needs on this device. The pair kernel takes
+// over once every CTA gets two or more wide tiles: its set-up cost is amortised and the operand
+// traffic it saves is what the wide kernel then waits for.
 enum Kernel { kNarrow = 0, kWide = 1, kPair = 2 };
 Kernel pick_kernel(int T, int B, int M) {
     const bool wide_ok = B % (256 / T) == 0;
@@ -926,6 +935,7 @@ Kernel pick_kernel(int T, int B, int M) {
     const long long t256 = t128 / 2;
     const long long rounds128 = (t128 + sms - 1) / sms;
     const long long rounds256 = (t256 + sms - 1) / sms;
+    if (pair_ok && t256 >= 2LL * sms) return kPair;
     return 10 * rounds256 < 9 * rounds128 ? kWide : kNarrow;     // a wide round costs ~1.1 narrow rounds
 }
 
