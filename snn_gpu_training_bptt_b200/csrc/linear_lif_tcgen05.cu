@@ -581,7 +581,7 @@ linear_lif_fwd_persistent_kernel(const __grid_constant__ CUtensorMap map_w, cons
 // pair's next tile. No multicast loads. All mbarrier waits are bounded as above; the cluster barriers at entry and
 // exit are reached unconditionally by every thread of both CTAs.
 // ---------------------------------------------------------------------------------------------
-constexpr int PAIR_STAGES = 4;
+constexpr int PAIR_STAGES = 5;
 constexpr uint32_t kPairTmemCols = 512;      // two accumulators of 256 columns: all of tensor memory
 constexpr int PAIR_N = 256;
 
