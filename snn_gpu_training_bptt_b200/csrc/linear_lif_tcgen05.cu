@@ -5,29 +5,35 @@
 //
 // In the reference this is `Fc` followed by `Fire`: T separate cuBLAS calls with a copy each
 // (fc_fp_cuda, snnlib/cuda/snn_kernel_fp.cu:332-357) and then fire_s_fp_kernel (:15-53) re-reading
-// the currents from HBM. Here one kernel computes a 128 (output neurons) x 128 (T time steps x
-// 128/T batch items) tile of currents in tensor memory and runs the recurrence on it in the
+// the currents from HBM. Here one kernel computes a tile of currents - 128 output neurons x
+// (T time steps x a group of batch items) - in tensor memory and runs the recurrence on it in the
 // epilogue, so spikes come straight out of the GEMM.
 //
 // GEMM orientation: D[m, n] = sum_k W[m, k] * X[n, k], M = output neurons, N = (t, b) pairs.
-// The X tile is fetched by one 3-D TMA box {64 k, 128/T batch items, T steps} of the [T][B][K]
-// tensor, which lands in shared memory as rows ordered (t major, b minor): accumulator column
-// n = t*(128/T) + j. A TMEM lane is one output neuron, so the epilogue thread that owns the lane
-// reads, for t = 0..T-1, the 128/T consecutive columns of that time step (tcgen05.ld 32x32b) and
-// carries u / gate of its 128/T batch items in registers across the T loads.
+// The X tile is fetched by one 3-D TMA box {64 k, BT batch items, T steps} of the [T][B][K]
+// tensor (BT = tile columns / T), which lands in shared memory as rows ordered (t major, b
+// minor): accumulator column n = t*BT + j. A TMEM lane is one output neuron, so the epilogue
+// thread that owns the lane reads the columns of its batch items step by step (tcgen05.ld
+// 32x32b) and carries their u / gate in registers across the T steps.
 //
-// Two kernels share the pieces below: a one-tile-per-CTA version and, the default, a persistent
-// version (further down) that overlaps the epilogue of one tile with the MMAs of the next and can
-// use 128 x 256 tiles (2 x 128/T batch items per tile) to halve the W traffic per flop.
+// Three kernels share the pieces below:
+//   * linear_lif_fwd_kernel            one 128 x 128 tile per CTA (the first version; fallback
+//                                      for outputs that are not 16-byte aligned)
+//   * linear_lif_fwd_persistent_kernel one CTA per SM walks a tile list; 128 x 128 or 128 x 256
+//                                      tiles; two accumulators so the epilogue of one tile
+//                                      overlaps the MMAs of the next; TMA-store epilogue
+//   * linear_lif_fwd_pair_kernel       a cluster of two CTAs per 256 x 256 tile with
+//                                      tcgen05.mma.cta_group::2; for layers with many tiles
+// pick_kernel() on the host chooses among them per problem.
 //
-// Pipeline (192 threads; the persistent kernels add a second epilogue group, warps 6-9): warp 4 =
-// TMA producer (one lane), warp 5 = MMA issuer (one lane, also owns the TMEM allocation), warps
-// 0-3 = epilogue (128 lanes of TMEM). STAGES shared-memory
-// stages of {W tile 128x64, X tile 128x64} bf16 with 128-byte swizzle; full/empty mbarriers per
-// stage; tcgen05.commit frees a stage when the MMAs that read it retire and finally signals the
-// accumulator. Every mbarrier wait is bounded (~1 s): on expiry the thread records an error code
-// in g_linear_lif_error, everybody falls through to the common exit, and TMEM is released.
-// No cluster launch, no multicast: every CTA fetches its own tiles.
+// Roles: warp 4 = TMA producer (one lane), warp 5 = MMA issuer (one lane, also owns the TMEM
+// allocation), warps 0-3 = epilogue (the 128 lanes of TMEM); the persistent and pair kernels add
+// a second epilogue group, warps 6-9. Shared-memory stages of {W tile, X tile} in bf16 with the
+// 128-byte swizzle; full/empty mbarriers per stage; tcgen05.commit frees a stage when the MMAs
+// that read it retire and finally signals the accumulator. Every mbarrier wait is bounded (~1 s):
+// on expiry the thread records an error code in g_linear_lif_error, everybody falls through to
+// the common exit, and TMEM is released. No multicast loads anywhere: every CTA fetches its own
+// operands.
 #include "../../include/snn_b200.h"
 
 #include <cuda.h>
