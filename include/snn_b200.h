@@ -211,6 +211,12 @@ int snn_channel_sum(const void *grad, float *out, int64_t outer, int64_t C, int6
  * with the device, and clears it when `reset` is non-zero.
  * -------------------------------------------------------------------------------------- */
 int snn_linear_lif_fwd_supported(int64_t T, int64_t B, int64_t K, int64_t M, int dtype);
+/* Which kernel snn_linear_lif_fwd runs for this problem on a device with `sm_count` SMs (no GPU
+ * needed, nothing launched; no counterpart in the reference): 0 = persistent kernel with 128 x 128
+ * tiles, 1 = with 128 x 256 tiles (the batch allows them and they save a round of tiles),
+ * 2 = CTA-pair kernel, 256 x 256 per pair (every CTA would get two or more wide tiles);
+ * -1 = unsupported problem. The environment override SNN_LINEAR_LIF_VARIANT is not applied. */
+int snn_linear_lif_fwd_plan(int64_t T, int64_t B, int64_t K, int64_t M, int dtype, int sm_count);
 int snn_linear_lif_fwd(const void *x, const void *weight, const float *bias, void *current,
                        void *spike, int64_t T, int64_t B, int64_t K, int64_t M, int dtype,
                        float alpha, float thresh, void *stream);

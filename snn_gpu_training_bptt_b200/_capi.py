@@ -31,6 +31,7 @@ SIGNATURES = {
     "snn_lif_pool_fwd": (_int, [_vp, _vp, _i64, _i64, _i64, _i64, _i64, _int, _f32, _f32, _vp]),
     "snn_lif_pool_bwd": (_int, [_vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _int, _f32, _f32, _f32, _f32, _vp]),
     "snn_linear_lif_fwd_supported": (_int, [_i64, _i64, _i64, _i64, _int]),
+    "snn_linear_lif_fwd_plan": (_int, [_i64, _i64, _i64, _i64, _int, _int]),
     "snn_linear_lif_fwd": (_int, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _int, _f32, _f32, _vp]),
     "snn_linear_lif_error": (_int, [_int]),
     "snn_channel_bias_add": (_int, [_vp, _vp, _i64, _i64, _i64, _int, _vp]),

@@ -928,14 +928,12 @@ int variant() {
 // over once every CTA gets two or more wide tiles: its set-up cost is amortised and the operand
 // traffic it saves is what the wide kernel then waits for.
 enum Kernel { kNarrow = 0, kWide = 1, kPair = 2 };
-Kernel pick_kernel(int T, int B, int M) {
+Kernel plan_kernel(int T, int B, int M, int sms, int forced) {
     const bool wide_ok = B % (256 / T) == 0;
     const bool pair_ok = wide_ok && M % (2 * BM) == 0;
-    const int v = variant();
-    if (v == 2 || !wide_ok) return kNarrow;
-    if (v == 3) return kWide;
-    if (v == 4) return pair_ok ? kPair : kWide;
-    const int sms = sm_count();
+    if (forced == 2 || !wide_ok) return kNarrow;
+    if (forced == 3) return kWide;
+    if (forced == 4) return pair_ok ? kPair : kWide;
     if (sms <= 0) return kNarrow;
     const long long t128 = static_cast<long long>(M / BM) * (B / (128 / T));
     const long long t256 = t128 / 2;
@@ -944,6 +942,7 @@ Kernel pick_kernel(int T, int B, int M) {
     if (pair_ok && t256 >= 2LL * sms) return kPair;
     return 10 * rounds256 < 9 * rounds128 ? kWide : kNarrow;     // a wide round costs ~1.1 narrow rounds
 }
+Kernel pick_kernel(int T, int B, int M) { return plan_kernel(T, B, M, sm_count(), variant()); }
 
 }  // namespace
 
@@ -956,6 +955,11 @@ int snn_linear_lif_fwd_supported(int64_t T, int64_t B, int64_t K, int64_t M, int
     if (K < BK || K % BK != 0 || M < BM || M % BM != 0) return 0;
     if (K > INT32_MAX || M > INT32_MAX) return 0;
     return 1;
+}
+
+int snn_linear_lif_fwd_plan(int64_t T, int64_t B, int64_t K, int64_t M, int dtype, int sm_count) {
+    if (!snn_linear_lif_fwd_supported(T, B, K, M, dtype) || sm_count < 1) return -1;
+    return static_cast<int>(plan_kernel(static_cast<int>(T), static_cast<int>(B), static_cast<int>(M), sm_count, 0));
 }
 
 int snn_linear_lif_fwd(const void* x, const void* weight, const float* bias, void* current, void* spike,

@@ -66,6 +66,29 @@ def test_argument_validation_needs_no_gpu(built_lib):
     assert L.snn_status_string(6).decode().startswith("workspace")
 
 
+def test_linear_lif_kernel_plan(built_lib):
+    """Kernel choice of the fused linear + LIF forward is host logic: no GPU needed. 0 = 128x128
+    tiles, 1 = 128x256 tiles, 2 = CTA pair, -1 = unsupported."""
+    from snn_gpu_training_bptt_b200 import _capi
+    L = _capi.lib()
+    BF16, F32 = 1, 0
+    plan = lambda T, B, K, M, sms=148, dt=BF16: L.snn_linear_lif_fwd_plan(T, B, K, M, dt, sms)
+    assert plan(8, 256, 2048, 2048) == 1             # the reference-sized layer: 128 wide tiles, one round
+    assert plan(8, 1024, 2048, 2048) == 2            # 512 wide tiles on 148 SMs: the pair takes over
+    assert plan(8, 4096, 2048, 2048) == 2
+    assert plan(8, 512, 2048, 2048) == 1             # 256 wide tiles < 2 per SM: still single CTAs
+    assert plan(8, 32, 256, 256) == 0                # everything fits in one round either way
+    assert plan(8, 48, 1024, 384) == 0               # batch not a multiple of 32: no wide tiles
+    assert plan(4, 64, 512, 128) == 0                # T=4 needs 64 batch items per wide tile; one round
+    assert plan(4, 1024, 256, 2048) == 1
+    assert plan(8, 2048, 128, 128 * 17) == 1         # odd number of 128-row tiles: no pair
+    assert plan(8, 1024, 2048, 2048, sms=16) == 2    # fewer SMs: more tiles each
+    assert plan(8, 256, 2048, 2048, sms=32) == 2
+    assert plan(8, 256, 2048, 2048, dt=F32) == -1
+    assert plan(6, 256, 2048, 2048) == -1
+    assert plan(8, 256, 2048, 2048, sms=0) == -1
+
+
 def test_missing_library_fails_loudly(monkeypatch, tmp_path):
     from snn_gpu_training_bptt_b200 import _capi
     monkeypatch.setattr(_capi, "_lib", None)
