@@ -204,9 +204,12 @@ int snn_channel_sum(const void *grad, float *out, int64_t outer, int64_t C, int6
  * snn_kernel_fp.cu:332-357, T cuBLAS calls) then fire_s_fp (snn.cpp:11-17).
  *   x [T, B, K] bf16, weight [M, K] bf16 (both 16-byte aligned), bias [M] fp32 or NULL,
  *   current [T, B, M] bf16 or NULL (the LIF input; backward re-reads it), spike [T, B, M] bf16.
- * Supported when snn_linear_lif_fwd_supported() returns 1: SNN_BF16, T in {4, 8},
- * B % (128/T) == 0, K % 64 == 0, M % 128 == 0; otherwise SNN_ERR_UNSUPPORTED (use snn_lif_fwd
- * after a library GEMM). Waits inside the kernel are bounded; snn_linear_lif_error() returns 0,
+ * Supported when snn_linear_lif_fwd_supported() returns 1: SNN_BF16, 2 <= T <= 16,
+ * B % (128/Tt) == 0 with Tt = the smallest of 2, 4, 8, 16 that is >= T (the kernels work on
+ * tiles of Tt steps; a tensor with fewer steps - the reference's default T is 6 - leaves the
+ * rest of the tile empty), K % 64 == 0, M % 128 == 0; otherwise SNN_ERR_UNSUPPORTED (use
+ * snn_lif_fwd after a library GEMM). Outputs that are not 16-byte aligned are accepted for
+ * T = 4 and T = 8 only (SNN_ERR_ALIGN otherwise). Waits inside the kernel are bounded; snn_linear_lif_error() returns 0,
  * or the code of the wait that expired (1 producer, 2 MMA issuer, 3 epilogue) after synchronising
  * with the device, and clears it when `reset` is non-zero.
  * -------------------------------------------------------------------------------------- */

@@ -417,7 +417,7 @@ def channel_sum(grad):
 # fused synaptic linear + LIF forward (tcgen05)
 # ----------------------------------------------------------------------------------------------
 def linear_lif_supported(x, weight):
-    """True if the tcgen05 kernel covers this problem (bf16, T in {4, 8}, tile-aligned sizes)."""
+    """True if the tcgen05 kernel covers this problem (bf16, 2 <= T <= 16, tile-aligned sizes)."""
     if x.dim() != 3 or weight.dim() != 2 or x.dtype != torch.bfloat16 or not x.is_cuda:
         return False
     T, B, K = x.shape
@@ -428,8 +428,8 @@ def linear_lif_fwd(x, weight, bias, alpha, thresh, want_current=True):
     """(current, spike) of ``LIF(x @ weight^T + bias)`` in one kernel. x [T, B, K] bf16, weight
     [M, K] (cast to bf16 if needed), bias fp32 [M] or None."""
     if not linear_lif_supported(x, weight):
-        raise ValueError("linear_lif_fwd: unsupported problem (needs bf16, T in {4, 8}, B % (128/T) == 0, "
-                         "K % 64 == 0, M % 128 == 0)")
+        raise ValueError("linear_lif_fwd: unsupported problem (needs bf16, 2 <= T <= 16, B a multiple of "
+                         "128 / (T rounded up to 2, 4, 8 or 16), K % 64 == 0, M % 128 == 0)")
     x = x.contiguous()
     w = weight.to(torch.bfloat16).contiguous()
     b = bias.float().contiguous() if bias is not None else None

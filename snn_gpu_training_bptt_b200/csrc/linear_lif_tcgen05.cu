@@ -41,6 +41,7 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 #include <stdlib.h>
+#include <type_traits>
 
 namespace snn_internal {
 void set_last_cuda_error(int e);   // defined in lif_capi.cu
@@ -330,18 +331,26 @@ __device__ __forceinline__ void group_barrier(int g) {      // the 128 threads o
     asm volatile("bar.sync %0, 128;" ::"r"(1 + g) : "memory");
 }
 
-// tcgen05.ld of NCOL (4 or 8) consecutive columns of this warp's 32 lanes into r[0..NCOL)
+// tcgen05.ld of NCOL (2, 4, 8 or 16) consecutive columns of this warp's 32 lanes into r[0..NCOL)
 template <int NCOL>
 __device__ __forceinline__ void tmem_ld_cols(uint32_t taddr, uint32_t* r) {
-    if constexpr (NCOL == 8) {
+    if constexpr (NCOL == 16) {
+        asm volatile(
+            "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+            : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+              "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+            : "r"(taddr));
+    } else if constexpr (NCOL == 8) {
         asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
                      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
                      : "r"(taddr));
-    } else {
-        static_assert(NCOL == 4, "4 or 8 columns");
+    } else if constexpr (NCOL == 4) {
         asm volatile("tcgen05.ld.sync.aligned.32x32b.x4.b32 {%0, %1, %2, %3}, [%4];"
                      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
                      : "r"(taddr));
+    } else {
+        static_assert(NCOL == 2, "2, 4, 8 or 16 columns");
+        asm volatile("tcgen05.ld.sync.aligned.32x32b.x2.b32 {%0, %1}, [%2];" : "=r"(r[0]), "=r"(r[1]) : "r"(taddr));
     }
 }
 // Waits for the loads issued so far. The 32 registers of a unit are passed through the statement
@@ -366,10 +375,13 @@ __device__ __forceinline__ void tmem_ld_wait32(uint32_t (&r)[32]) {
 // of shared memory while the next unit is computed into the other buffer. `k` counts the units
 // this group has staged since the kernel started (buffer = k & 1). `drained()` is called by every
 // thread once its last TMEM read of the tile has completed. On entry the accumulator is full.
-template <int T, int WN, typename Drained>
+// T is the tile's step count (2, 4, 8 or 16); the tensor has t_real <= T steps: the steps beyond
+// are zero-filled by the TMA loads, skipped here and clipped by the TMA stores (FULL = the tensor
+// fills the tile, no step is checked).
+template <int T, int WN, bool FULL, typename Drained>
 __device__ __forceinline__ void lif_epilogue_tile(EpilogueStaging (&stage)[2], int& k, int g, bool elected,
                                                   uint32_t lane_base, int row, float bias_m, float alpha,
-                                                  float thresh, const CUtensorMap* map_spike,
+                                                  float thresh, int t_real, const CUtensorMap* map_spike,
                                                   const CUtensorMap* map_current, int write_current, int m0,
                                                   int b0, Drained&& drained)
 {
@@ -398,6 +410,7 @@ __device__ __forceinline__ void lif_epilogue_tile(EpilogueStaging (&stage)[2], i
         for (int j = 0; j < SB; ++j) { u[j] = 0.f; gate[j] = 1.f; }
 #pragma unroll
         for (int t = 0; t < T; ++t) {
+            if (!FULL && t >= t_real) break;
 #pragma unroll
             for (int j = 0; j < SB; ++j) {
                 const int n = t * SB + j;
@@ -430,7 +443,8 @@ __global__ void __launch_bounds__(kThreadsP, 1)
 linear_lif_fwd_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                                  const __grid_constant__ CUtensorMap map_spike,
                                  const __grid_constant__ CUtensorMap map_current, int write_current,
-                                 const float* __restrict__ bias, int B, int K, int M, float alpha, float thresh)
+                                 const float* __restrict__ bias, int B, int K, int M, float alpha, float thresh,
+                                 int t_real)
 {
     constexpr int BT = WN / T;                  // batch items per tile
     constexpr int PSTAGES = PersistentCfg<WN>::kStages;
@@ -547,8 +561,13 @@ linear_lif_fwd_persistent_kernel(const __grid_constant__ CUtensorMap map_w, cons
             const float bias_m = bias != nullptr ? bias[m0 + row] : 0.f;
             const uint32_t lane_base = tmem_base + buf * WN + (static_cast<uint32_t>(quarter * 32) << 16);
             uint64_t* drained_bar = &sm.acc_empty[buf];
-            lif_epilogue_tile<T, WN>(sm.epi[g], staged, g, elected, lane_base, row, bias_m, alpha, thresh, &map_spike,
-                                     &map_current, write_current, m0, b0, [drained_bar] { mbar_arrive(drained_bar); });
+            auto drained = [drained_bar] { mbar_arrive(drained_bar); };
+            if (t_real == T)
+                lif_epilogue_tile<T, WN, true>(sm.epi[g], staged, g, elected, lane_base, row, bias_m, alpha, thresh,
+                                               t_real, &map_spike, &map_current, write_current, m0, b0, drained);
+            else
+                lif_epilogue_tile<T, WN, false>(sm.epi[g], staged, g, elected, lane_base, row, bias_m, alpha, thresh,
+                                                t_real, &map_spike, &map_current, write_current, m0, b0, drained);
         }
         // shared memory must outlive the reads of the last stores; the writes themselves complete
         // before the grid does
@@ -658,7 +677,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreadsP, 1)
 linear_lif_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                            const __grid_constant__ CUtensorMap map_spike,
                            const __grid_constant__ CUtensorMap map_current, int write_current,
-                           const float* __restrict__ bias, int B, int K, int M, float alpha, float thresh)
+                           const float* __restrict__ bias, int B, int K, int M, float alpha, float thresh,
+                           int t_real)
 {
     constexpr int BT = PAIR_N / T;              // batch items per tile
     extern __shared__ __align__(1024) unsigned char smem_raw[];
@@ -772,9 +792,13 @@ linear_lif_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
             const float bias_m = bias != nullptr ? bias[m0 + row] : 0.f;
             const uint32_t lane_base = tmem_base + buf * PAIR_N + (static_cast<uint32_t>(quarter * 32) << 16);
             const uint32_t acc_empty_leader = buf ? acc_empty_leader1 : acc_empty_leader0;
-            lif_epilogue_tile<T, PAIR_N>(sm.epi[g], staged, g, elected, lane_base, row, bias_m, alpha, thresh, &map_spike,
-                                         &map_current, write_current, m0, b0,
-                                         [acc_empty_leader] { mbar_arrive_cluster(acc_empty_leader); });
+            auto drained = [acc_empty_leader] { mbar_arrive_cluster(acc_empty_leader); };
+            if (t_real == T)
+                lif_epilogue_tile<T, PAIR_N, true>(sm.epi[g], staged, g, elected, lane_base, row, bias_m, alpha, thresh,
+                                                   t_real, &map_spike, &map_current, write_current, m0, b0, drained);
+            else
+                lif_epilogue_tile<T, PAIR_N, false>(sm.epi[g], staged, g, elected, lane_base, row, bias_m, alpha, thresh,
+                                                    t_real, &map_spike, &map_current, write_current, m0, b0, drained);
         }
         if (elected) SNN_TRACE(43 + 10 * g);
         if (elected) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
@@ -875,7 +899,7 @@ int sm_count() {
 template <int T, int WN>
 int launch_persistent(const CUtensorMap& mw, const CUtensorMap& mx, const CUtensorMap& ms, const CUtensorMap& mc,
                       int write_current, const float* bias, int B, int K, int M, float alpha, float thresh,
-                      cudaStream_t st) {
+                      int t_real, cudaStream_t st) {
     static_assert(sizeof(PersistentStorage<WN>) + 1024 <= 227 * 1024, "shared memory budget");
     const size_t smem = sizeof(PersistentStorage<WN>) + 1024;
     auto kern = linear_lif_fwd_persistent_kernel<T, WN>;
@@ -885,7 +909,7 @@ int launch_persistent(const CUtensorMap& mw, const CUtensorMap& mx, const CUtens
     if (e != cudaSuccess) { snn_internal::set_last_cuda_error(static_cast<int>(e)); return SNN_ERR_CUDA; }
     const int tiles = (M / BM) * (B / (WN / T));
     const int grid = tiles < sms ? tiles : sms;
-    kern<<<grid, kThreadsP, smem, st>>>(mw, mx, ms, mc, write_current, bias, B, K, M, alpha, thresh);
+    kern<<<grid, kThreadsP, smem, st>>>(mw, mx, ms, mc, write_current, bias, B, K, M, alpha, thresh, t_real);
     e = cudaGetLastError();
     if (e != cudaSuccess) { snn_internal::set_last_cuda_error(static_cast<int>(e)); return SNN_ERR_CUDA; }
     return SNN_OK;
@@ -894,7 +918,7 @@ int launch_persistent(const CUtensorMap& mw, const CUtensorMap& mx, const CUtens
 template <int T>
 int launch_pair(const CUtensorMap& mw, const CUtensorMap& mx, const CUtensorMap& ms, const CUtensorMap& mc,
                 int write_current, const float* bias, int B, int K, int M, float alpha, float thresh,
-                cudaStream_t st) {
+                int t_real, cudaStream_t st) {
     static_assert(sizeof(PairStorage) + 1024 <= 227 * 1024, "shared memory budget");
     const size_t smem = sizeof(PairStorage) + 1024;
     auto kern = linear_lif_fwd_pair_kernel<T>;
@@ -904,7 +928,7 @@ int launch_pair(const CUtensorMap& mw, const CUtensorMap& mx, const CUtensorMap&
     if (e != cudaSuccess) { snn_internal::set_last_cuda_error(static_cast<int>(e)); return SNN_ERR_CUDA; }
     const int tiles = (M / (2 * BM)) * (B / (PAIR_N / T));
     const int pairs = tiles < sms / 2 ? tiles : sms / 2;
-    kern<<<2 * pairs, kThreadsP, smem, st>>>(mw, mx, ms, mc, write_current, bias, B, K, M, alpha, thresh);
+    kern<<<2 * pairs, kThreadsP, smem, st>>>(mw, mx, ms, mc, write_current, bias, B, K, M, alpha, thresh, t_real);
     e = cudaGetLastError();
     if (e != cudaSuccess) { snn_internal::set_last_cuda_error(static_cast<int>(e)); return SNN_ERR_CUDA; }
     return SNN_OK;
@@ -927,7 +951,25 @@ int variant() {
 // count, so compare the rounds of tiles each choice needs on this device. The pair kernel takes
 // over once every CTA gets two or more wide tiles: its set-up cost is amortised and the operand
 // traffic it saves is what the wide kernel then waits for.
+// Step count of the tile that holds a tensor of T steps: the kernels are compiled for 2, 4, 8 and
+// 16; other T (the reference's default is 6) run in the next larger tile with the missing steps
+// zero-filled, at T / tile of the tensor-core efficiency.
+int tile_steps(int64_t T) { return T <= 2 ? 2 : (T <= 4 ? 4 : (T <= 8 ? 8 : 16)); }
+// the one-tile-per-CTA kernel exists for full tiles of 4 and 8 steps only
+bool one_tile_kernel_covers(int64_t T) { return T == 4 || T == 8; }
+
+template <typename F>
+int with_tile_steps(int steps, F&& f) {
+    switch (steps) {
+        case 2: return f(std::integral_constant<int, 2>{});
+        case 4: return f(std::integral_constant<int, 4>{});
+        case 8: return f(std::integral_constant<int, 8>{});
+        default: return f(std::integral_constant<int, 16>{});
+    }
+}
+
 enum Kernel { kNarrow = 0, kWide = 1, kPair = 2 };
+// T here is the tile's step count
 Kernel plan_kernel(int T, int B, int M, int sms, int forced) {
     const bool wide_ok = B % (256 / T) == 0;
     const bool pair_ok = wide_ok && M % (2 * BM) == 0;
@@ -942,7 +984,7 @@ Kernel plan_kernel(int T, int B, int M, int sms, int forced) {
     if (pair_ok && t256 >= 2LL * sms) return kPair;
     return 10 * rounds256 < 9 * rounds128 ? kWide : kNarrow;     // a wide round costs ~1.1 narrow rounds
 }
-Kernel pick_kernel(int T, int B, int M) { return plan_kernel(T, B, M, sm_count(), variant()); }
+Kernel pick_kernel(int tile_t, int B, int M) { return plan_kernel(tile_t, B, M, sm_count(), variant()); }
 
 }  // namespace
 
@@ -950,16 +992,17 @@ extern "C" {
 
 int snn_linear_lif_fwd_supported(int64_t T, int64_t B, int64_t K, int64_t M, int dtype) {
     if (dtype != SNN_BF16) return 0;
-    if (T != 4 && T != 8) return 0;          // 128/T batch items per tile, read 16 columns at a time
-    if (B < 1 || B % (BN / T) != 0 || B > 65535 * (BN / T)) return 0;
+    if (T < 2 || T > 16) return 0;
+    const int bt = BN / tile_steps(T);       // batch items per 128-column tile
+    if (B < 1 || B % bt != 0 || B > 65535LL * bt) return 0;
     if (K < BK || K % BK != 0 || M < BM || M % BM != 0) return 0;
-    if (K > INT32_MAX || M > INT32_MAX) return 0;
+    if (K > INT32_MAX || M > INT32_MAX || B > INT32_MAX) return 0;
     return 1;
 }
 
 int snn_linear_lif_fwd_plan(int64_t T, int64_t B, int64_t K, int64_t M, int dtype, int sm_count) {
     if (!snn_linear_lif_fwd_supported(T, B, K, M, dtype) || sm_count < 1) return -1;
-    return static_cast<int>(plan_kernel(static_cast<int>(T), static_cast<int>(B), static_cast<int>(M), sm_count, 0));
+    return static_cast<int>(plan_kernel(tile_steps(T), static_cast<int>(B), static_cast<int>(M), sm_count, 0));
 }
 
 int snn_linear_lif_fwd(const void* x, const void* weight, const float* bias, void* current, void* spike,
@@ -972,18 +1015,21 @@ int snn_linear_lif_fwd(const void* x, const void* weight, const float* bias, voi
     auto al = [](const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; };
     if (!al(x, 16) || !al(weight, 16) || !al(spike, 2) || !al(current, 2) || !al(bias, 4)) return SNN_ERR_ALIGN;
 
-    const bool one_tile = variant() == 1 || !al(spike, 16) || !al(current, 16);
-    const Kernel kernel = one_tile ? kNarrow : pick_kernel(static_cast<int>(T), static_cast<int>(B), static_cast<int>(M));
+    const int Tt = tile_steps(T), Ti = static_cast<int>(T);
+    const bool bulk_stores_ok = al(spike, 16) && al(current, 16);      // the persistent kernels store by TMA
+    if (!bulk_stores_ok && !one_tile_kernel_covers(T)) return SNN_ERR_ALIGN;
+    const bool one_tile = !bulk_stores_ok || (variant() == 1 && one_tile_kernel_covers(T));
+    const Kernel kernel = one_tile ? kNarrow : pick_kernel(Tt, static_cast<int>(B), static_cast<int>(M));
     const cuuint32_t tile_n = kernel == kNarrow ? 128 : 256;
     // a pair member fetches half of the tile's time steps
-    const cuuint32_t tile_t = static_cast<cuuint32_t>(kernel == kPair ? T / 2 : T);
+    const cuuint32_t box_t = static_cast<cuuint32_t>(kernel == kPair ? Tt / 2 : Tt);
     CUtensorMap mw, mx;
     const cuuint64_t wdims[2] = {static_cast<cuuint64_t>(K), static_cast<cuuint64_t>(M)};
     const cuuint64_t wstr[1] = {static_cast<cuuint64_t>(K) * 2};
     const cuuint32_t wbox[2] = {BK, BM};
     const cuuint64_t xdims[3] = {static_cast<cuuint64_t>(K), static_cast<cuuint64_t>(B), static_cast<cuuint64_t>(T)};
     const cuuint64_t xstr[2] = {static_cast<cuuint64_t>(K) * 2, static_cast<cuuint64_t>(B) * K * 2};
-    const cuuint32_t xbox[3] = {BK, tile_n / static_cast<cuuint32_t>(T), tile_t};
+    const cuuint32_t xbox[3] = {BK, tile_n / static_cast<cuuint32_t>(Tt), box_t};
     if (!cached_map(&mw, weight, 2, wdims, wstr, wbox) || !cached_map(&mx, x, 3, xdims, xstr, xbox)) {
         snn_internal::set_last_cuda_error(static_cast<int>(cudaErrorInvalidValue));
         return SNN_ERR_CUDA;
@@ -997,7 +1043,7 @@ int snn_linear_lif_fwd(const void* x, const void* weight, const float* bias, voi
     CUtensorMap ms, mc;
     const cuuint64_t odims[3] = {static_cast<cuuint64_t>(M), static_cast<cuuint64_t>(B), static_cast<cuuint64_t>(T)};
     const cuuint64_t ostr[2] = {static_cast<cuuint64_t>(M) * 2, static_cast<cuuint64_t>(B) * M * 2};
-    const cuuint32_t obox[3] = {BM, static_cast<cuuint32_t>(32 / T), static_cast<cuuint32_t>(T)};   // one epilogue unit
+    const cuuint32_t obox[3] = {BM, static_cast<cuuint32_t>(32 / Tt), static_cast<cuuint32_t>(Tt)};   // one epilogue unit
     if (!cached_map(&ms, spike, 3, odims, ostr, obox, false) ||
         (current != nullptr && !cached_map(&mc, current, 3, odims, ostr, obox, false))) {
         snn_internal::set_last_cuda_error(static_cast<int>(cudaErrorInvalidValue));
@@ -1005,16 +1051,12 @@ int snn_linear_lif_fwd(const void* x, const void* weight, const float* bias, voi
     }
     if (current == nullptr) mc = ms;
     const int wc = current != nullptr ? 1 : 0;
-    if (kernel == kPair) {
-        if (T == 4) return launch_pair<4>(mw, mx, ms, mc, wc, bias, Bi, Ki, Mi, alpha, thresh, st);
-        return launch_pair<8>(mw, mx, ms, mc, wc, bias, Bi, Ki, Mi, alpha, thresh, st);
-    }
-    if (kernel == kWide) {
-        if (T == 4) return launch_persistent<4, 256>(mw, mx, ms, mc, wc, bias, Bi, Ki, Mi, alpha, thresh, st);
-        return launch_persistent<8, 256>(mw, mx, ms, mc, wc, bias, Bi, Ki, Mi, alpha, thresh, st);
-    }
-    if (T == 4) return launch_persistent<4, 128>(mw, mx, ms, mc, wc, bias, Bi, Ki, Mi, alpha, thresh, st);
-    return launch_persistent<8, 128>(mw, mx, ms, mc, wc, bias, Bi, Ki, Mi, alpha, thresh, st);
+    return with_tile_steps(Tt, [&](auto steps) {
+        constexpr int S = decltype(steps)::value;
+        if (kernel == kPair) return launch_pair<S>(mw, mx, ms, mc, wc, bias, Bi, Ki, Mi, alpha, thresh, Ti, st);
+        if (kernel == kWide) return launch_persistent<S, 256>(mw, mx, ms, mc, wc, bias, Bi, Ki, Mi, alpha, thresh, Ti, st);
+        return launch_persistent<S, 128>(mw, mx, ms, mc, wc, bias, Bi, Ki, Mi, alpha, thresh, Ti, st);
+    });
 }
 
 #ifdef SNN_LINEAR_LIF_TRACE

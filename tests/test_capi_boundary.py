@@ -85,7 +85,13 @@ def test_linear_lif_kernel_plan(built_lib):
     assert plan(8, 1024, 2048, 2048, sms=16) == 2    # fewer SMs: more tiles each
     assert plan(8, 256, 2048, 2048, sms=32) == 2
     assert plan(8, 256, 2048, 2048, dt=F32) == -1
-    assert plan(6, 256, 2048, 2048) == -1
+    assert plan(6, 256, 2048, 2048) == 1             # 6 steps run in the 8-step tile
+    assert plan(16, 512, 128, 2048) == 2
+    assert plan(2, 128, 128, 128) == 0
+    assert plan(3, 64, 64, 128) == 0
+    assert plan(3, 48, 64, 128) == -1                # 4-step tile: batch must be a multiple of 32
+    assert plan(1, 256, 2048, 2048) == -1
+    assert plan(17, 256, 2048, 2048) == -1
     assert plan(8, 256, 2048, 2048, sms=0) == -1
 
 

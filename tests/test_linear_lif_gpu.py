@@ -40,7 +40,10 @@ def make(T, B, K, M, seed):
 # The last three shapes are large enough for the 256-column tiles (the second of them gives every
 # CTA several wide tiles, the third is T=4 with 64 batch items per tile).
 SHAPES = [(8, 16, 64, 128), (8, 32, 256, 256), (4, 32, 128, 128), (8, 48, 1024, 384), (4, 64, 512, 128),
-          (8, 256, 2048, 2048), (8, 1024, 128, 2048), (4, 1024, 256, 2048)]
+          (8, 256, 2048, 2048), (8, 1024, 128, 2048), (4, 1024, 256, 2048),
+          # step counts that do not fill a 2 / 4 / 8 / 16-step tile (6 is the reference's default), and 2 / 16
+          (6, 64, 256, 256), (6, 256, 1024, 2048), (3, 64, 64, 128), (2, 128, 128, 128), (16, 64, 128, 256),
+          (12, 32, 64, 256), (16, 512, 128, 2048), (5, 1024, 64, 2048)]
 
 
 @pytest.mark.parametrize("shape", SHAPES)
@@ -87,9 +90,12 @@ def test_unsupported_problems_are_reported(capi):
     x, w, b = make(8, 16, 64, 128, seed=1)
     assert not capi.linear_lif_supported(x.float(), w)
     assert not capi.linear_lif_supported(x[:, :15], w)              # B not a multiple of 16
-    assert not capi.linear_lif_supported(x[:6], w)                  # T = 6
+    assert capi.linear_lif_supported(x[:6], w)                      # T = 6 runs in an 8-step tile
+    assert not capi.linear_lif_supported(x[:1], w)                  # T = 1
+    x17 = torch.cat([x, x, x[:1]])                                  # T = 17
+    assert not capi.linear_lif_supported(x17, w)
     with pytest.raises(ValueError):
-        capi.linear_lif_fwd(x[:6].contiguous(), w, b, A, TH)
+        capi.linear_lif_fwd(x17, w, b, A, TH)
     L = capi.lib()
     assert L.snn_linear_lif_fwd_supported(8, 16, 64, 128, 1) == 1
     assert L.snn_linear_lif_fwd_supported(8, 16, 96, 128, 1) == 0
