@@ -102,3 +102,55 @@ def test_failed_rank_surfaces_as_error_not_hang(tmp_path):
     res = _run(tmp_path, 25.0, fail_rank=1)
     assert res[1]["status"].startswith("error: RuntimeError: injected")
     assert res[0]["status"].startswith("error")
+
+
+def _syncbn_worker(rank, world, port, out_dir):
+    sys.path.insert(0, ROOT)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    import datetime
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=60))
+    from snn_gpu_training_bptt_b200 import snnlib_op as sop
+    torch.set_num_threads(1)
+    gen = torch.Generator().manual_seed(11)
+    full = torch.randn(4, 2 * world, 6, 3, 3, generator=gen) * 2 + 0.5        # [T, B_total, C, H, W]
+    mine = full[:, rank * 2:(rank + 1) * 2].contiguous()
+    layer = sop.BnDist(6, (0, 1, 3, 4))
+    var1, mean1 = layer._statistics(mine)
+    var2, mean2 = layer._statistics(mine * 0.5)                                # second step: running stats move on
+    torch.save({"var1": var1, "mean1": mean1, "var2": var2, "mean2": mean2,
+                "running_var": layer.running_var.detach().clone(),
+                "running_mean": layer.running_mean.detach().clone(),
+                "world": layer.world_size, "ids": (id(layer.running_var), id(layer.running_mean))},
+               os.path.join(out_dir, f"bn{rank}.pt"))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_sync_bn_statistics_over_two_ranks(tmp_path):
+    """Host side of the sync-BN layers (reference snnlib_op.py:231-282): every rank normalises with
+    the statistics of the whole batch (mean of the ranks' means and mean squares), and the running
+    statistics follow the reference's update (momentum 0.05, unbiased correction with the LOCAL
+    element count, as the reference computes its factor from the local tensor)."""
+    world, port = 2, _free_port()
+    mp.spawn(_syncbn_worker, args=(world, port, str(tmp_path)), nprocs=world, join=True)
+    res = [torch.load(os.path.join(tmp_path, f"bn{r}.pt")) for r in range(world)]
+    gen = torch.Generator().manual_seed(11)
+    full = torch.randn(4, 2 * world, 6, 3, 3, generator=gen) * 2 + 0.5
+    dims = (0, 1, 3, 4)
+    var_all, mean_all = torch.var_mean(full, dim=dims, unbiased=False)
+    for r in res:
+        assert r["world"] == world
+        assert torch.allclose(r["mean1"], mean_all, atol=1e-6)
+        assert torch.allclose(r["var1"], var_all, rtol=1e-5, atol=1e-6)
+        assert torch.allclose(r["mean2"], mean_all * 0.5, atol=1e-6)
+        assert torch.allclose(r["var2"], var_all * 0.25, rtol=1e-5, atol=1e-6)
+    count = full.numel() / world / 6                         # local elements per channel
+    factor = count / (count - 1)
+    rv, rm = torch.ones(6), torch.zeros(6)
+    for scale in (1.0, 0.5):
+        rv = rv * 0.95 + var_all * scale * scale * (0.05 * factor)
+        rm = rm * 0.95 + mean_all * scale * 0.05
+    for r in res:
+        assert torch.allclose(r["running_var"], rv, rtol=1e-5, atol=1e-6)
+        assert torch.allclose(r["running_mean"], rm, rtol=1e-5, atol=1e-6)
+    assert torch.equal(res[0]["running_var"], res[1]["running_var"])
