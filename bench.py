@@ -41,7 +41,7 @@ WORKLOAD = "lif_fire_fwd_bwd fp32 T=8 N=2^26 per GPU, x~N(0.5,1), grad~N(0,1), s
 # DRAM traffic of the backward kernel per neuron-timestep as measured by one ncu capture
 # (dram__bytes_read.sum + dram__bytes_write.sum of snn::lif_bwd_kernel, T=8, N=2^24 -- 2 GiB on
 # the device, inside the capture size rule -- divided by T*N; traffic is proportional to T*N,
-# so a full launch is this figure x T*N). See profiles/.
+# so a full launch is this figure x T*N).
 NCU_BWD_TRAFFIC_BYTES_PER_STEP = 11.69
 
 

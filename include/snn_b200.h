@@ -3,8 +3,11 @@
  * of liangling76/snn_gpu_training_bptt's `snnlib`, as hand-written sm_100a kernels.
  *
  * Conventions
- *   - plain C types only; every buffer is DEVICE memory owned by the caller; nothing is
- *     allocated, cached or freed by the library; outputs are written in full;
+ *   - plain C types only; every buffer is DEVICE memory owned by the caller; outputs are
+ *     written in full; the library never calls cudaMalloc / cudaFree. The only state it keeps
+ *     between calls is documented where it applies: the 64 MiB built-in scratch array and its
+ *     cached device address (snn_lif_bwd_noalloc), and a small host-side cache of encoded
+ *     tensor maps plus a device error word (snn_linear_lif_*);
  *   - tensors are time-major and contiguous: [T, N] with element (t, n) at t*N + n, where
  *     N = B*C*H*W is the reference's per-time-step element count (its `BCHW`,
  *     snnlib/cuda/snn_kernel_fp.cu:60-63); neurons are independent, so B and CHW need not
@@ -246,8 +249,10 @@ int snn_linear_lif_error(int reset);
  *     returned and nothing is launched (e.g. fp32: T*N <= 16 Mi neuron-steps; split the neuron
  *     axis into several calls for more);
  *   - the first call on each device looks up the array's device address (one
- *     cudaGetSymbolAddress, with that device current). Make that first call during set-up,
- *     before any stream capture is begun on that device;
+ *     cudaGetSymbolAddress, with that device current) and caches it for the life of the
+ *     process. Make that first call during set-up, before any stream capture is begun on that
+ *     device. A cudaDeviceReset() invalidates the cached address: do not call this entry point
+ *     on a device after resetting it;
  *   - all calls on one GPU share the one array. It keeps whatever the previous call left; this
  *     entry point overwrites every element it later reads, so nothing needs clearing, but two
  *     calls that can overlap on the GPU (different streams, no dependency) race on it. Issue

@@ -59,32 +59,5 @@ def build(force: bool = False, verbose: bool = False) -> str:
     return LIB
 
 
-def build_tuner(cache_policy=None) -> str:
-    """Build csrc/tune/lif_tune (stand-alone launch-configuration tuner; needs a GPU to run)."""
-    out = os.path.join(CSRC, "tune", "lif_tune")
-    nvcc = os.environ.get("NVCC", "nvcc")
-    cmd = [nvcc, "-O3", "-std=c++17", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo"]
-    if cache_policy is not None:
-        cmd.append(f"-DSNN_CACHE_POLICY={int(cache_policy)}")
-    subprocess.run(cmd + ["-o", out, os.path.join(CSRC, "tune", "lif_tune.cu")], check=True)
-    return out
-
-
-def build_trace() -> str:
-    """Build csrc/tune/linear_lif_trace (phase timeline of the fused linear + LIF kernels; needs a GPU to run)."""
-    out = os.path.join(CSRC, "tune", "linear_lif_trace")
-    nvcc = os.environ.get("NVCC", "nvcc")
-    cmd = [nvcc, "-O3", "-std=c++17", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo",
-           "-diag-suppress", "177"]
-    subprocess.run(cmd + ["-o", out, os.path.join(CSRC, "tune", "linear_lif_trace.cu")], check=True)
-    return out
-
-
 if __name__ == "__main__":
-    if "--trace" in sys.argv:
-        print(build_trace())
-    elif "--tuner" in sys.argv:
-        pol = sys.argv[sys.argv.index("--cache-policy") + 1] if "--cache-policy" in sys.argv else None
-        print(build_tuner(pol))
-    else:
-        print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv))
+    print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv))

@@ -169,7 +169,8 @@ int snn_bn_lif_bwd_sums(const void* x, const void* grad, const float* weight, co
         using IO = decltype(tag);
         auto smem_for = [&](int VEC, int* nq) {
             const long long span = static_cast<long long>(kBlock) * VEC;
-            *nq = static_cast<int>((span + inner - 1) / inner + 1);
+            const long long runs = (span + inner - 1) / inner + 1;    // channel runs a CTA can touch
+            *nq = static_cast<int>(runs < C ? runs : C);             // more runs than channels: one slot per channel
             return 2 * sizeof(float) * static_cast<size_t>(*nq);
         };
         if (!fire) {

@@ -192,7 +192,11 @@ __device__ __forceinline__ void bn_lif_grad_current(const Pack<IO, VEC> (&xin)[T
 //                     butterfly, then one global atomicAdd pair per warp; no shared memory.
 //   WARP_RUN = false: shared-memory accumulators, one slot per channel run a CTA can touch
 //                     (dynamic shared memory 2*nq floats, nq = (span + inner - 1)/inner + 1),
-//                     then one global atomicAdd pair per (CTA, run).
+//                     then one global atomicAdd pair per (CTA, run). When a CTA touches more runs
+//                     than there are channels (short runs: channels-last images and [T,B,C]
+//                     inputs have inner = 1, every neuron its own run) the slots are indexed by
+//                     channel instead (nq = C, slot = (run - first run) mod C), so the CTA still
+//                     reduces in shared memory and issues at most C global atomic pairs.
 // ---------------------------------------------------------------------------------------
 // EXACT = (T == TMAX): the time loops then carry no per-step bound checks.
 template <typename IO, int VEC, int TMAX, bool FIRE, bool WARP_RUN, bool EXACT>
@@ -261,6 +265,13 @@ __device__ __forceinline__ void bn_lif_bwd_sums_body(const IO* __restrict__ x, c
         return;
     }
 
+    // slot of a run: its offset from the CTA's first run, folded onto the channels when the CTA
+    // covers more runs than channels (nq == C then, and slot j belongs to channel_of_run(q0 + j))
+    const bool by_channel = nq == p.C;
+    auto slot_of = [&](long long run) {
+        const unsigned int d = static_cast<unsigned int>(run - q0);
+        return static_cast<int>(by_channel ? d % static_cast<unsigned int>(nq) : d);
+    };
     // warp inside one channel run: butterfly, one shared atomic per warp; otherwise per lane
     const long long q_first = __shfl_sync(0xffffffffu, q[0], 0);
     const bool same = __all_sync(0xffffffffu, (!active) || (q[0] == q_first && q[VEC - 1] == q_first));
@@ -274,14 +285,14 @@ __device__ __forceinline__ void bn_lif_bwd_sums_body(const IO* __restrict__ x, c
             c2 += __shfl_xor_sync(0xffffffffu, c2, o);
         }
         if ((threadIdx.x & 31) == 0) {
-            const int j = static_cast<int>(q_first - q0);
+            const int j = slot_of(q_first);
             atomicAdd(&sacc[j], a);
             atomicAdd(&sacc[nq + j], c2);
         }
     } else if (active) {
 #pragma unroll
         for (int v = 0; v < VEC; ++v) {
-            const int j = static_cast<int>(q[v] - q0);
+            const int j = slot_of(q[v]);
             atomicAdd(&sacc[j], s1[v]);
             atomicAdd(&sacc[nq + j], s2[v]);
         }

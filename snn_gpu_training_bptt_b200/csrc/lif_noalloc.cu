@@ -17,6 +17,7 @@
 #include "../../include/snn_b200.h"
 #include "lif_kernels.cuh"
 
+#include <atomic>
 #include <mutex>
 
 static __device__ __align__(256) unsigned char g_membrane_scratch[SNN_STATIC_SCRATCH_BYTES];
@@ -31,10 +32,12 @@ constexpr int kBlock = 256;
 constexpr int kMaxDevices = 64;
 
 std::mutex g_setup_mutex;
-void* g_scratch_address[kMaxDevices] = {};
+std::atomic<void*> g_scratch_address[kMaxDevices] = {};
 
 // Device address of g_membrane_scratch on the CURRENT device (looked up on the first call for
-// that device, then cached). Returns nullptr and records the CUDA error on failure.
+// that device, then cached; later calls read the cached pointer without taking the mutex).
+// Returns nullptr and records the CUDA error on failure. A cudaDeviceReset() invalidates the
+// cached address: a process that resets a device must not call this entry point on it again.
 void* scratch_on_current_device() {
     int dev = -1;
     cudaError_t e = cudaGetDevice(&dev);
@@ -43,17 +46,19 @@ void* scratch_on_current_device() {
         snn_internal::set_last_cuda_error(static_cast<int>(e));
         return nullptr;
     }
+    void* ptr = g_scratch_address[dev].load(std::memory_order_acquire);
+    if (ptr != nullptr) return ptr;
     std::lock_guard<std::mutex> lock(g_setup_mutex);
-    if (g_scratch_address[dev] == nullptr) {
-        void* ptr = nullptr;
+    ptr = g_scratch_address[dev].load(std::memory_order_relaxed);
+    if (ptr == nullptr) {
         e = cudaGetSymbolAddress(&ptr, g_membrane_scratch);
         if (e != cudaSuccess || ptr == nullptr) {
             snn_internal::set_last_cuda_error(static_cast<int>(e));
             return nullptr;
         }
-        g_scratch_address[dev] = ptr;
+        g_scratch_address[dev].store(ptr, std::memory_order_release);
     }
-    return g_scratch_address[dev];
+    return ptr;
 }
 
 inline bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }

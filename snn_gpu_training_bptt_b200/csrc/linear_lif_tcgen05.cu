@@ -62,19 +62,6 @@ constexpr long long kWaitCycles = 2000000000LL;       // ~1 s
 
 __device__ int g_linear_lif_error = 0;
 
-// Phase stamps for csrc/tune/linear_lif_trace.cu (built with -DSNN_LINEAR_LIF_TRACE): slot <- the
-// SM's cycle counter, one row per CTA. Compiled out of the library.
-#ifdef SNN_LINEAR_LIF_TRACE
-constexpr int kTraceSlots = 64;
-__device__ long long g_linear_lif_trace[1024][kTraceSlots];
-#define SNN_TRACE(slot) do { if (blockIdx.x < 1024) g_linear_lif_trace[blockIdx.x][slot] = clock64(); } while (0)
-#else
-#define SNN_TRACE(slot) do { } while (0)
-#endif
-// slots: 0..39 = operands of K stage i of the CTA's first tile seen by the MMA issuer, 40 = accumulator of
-// the first tile committed, 42 / 52 = epilogue group 0 / 1 sees the first accumulator, 43 / 53 = group has
-// issued its last store, 44 / 54 = that store has been read out, 45 = kernel entry, 46 = set-up done
-
 struct __align__(1024) SharedStorage {
     __nv_bfloat16 a[STAGES][BM * BK];
     __nv_bfloat16 b[STAGES][BN * BK];
@@ -105,12 +92,20 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
-// false if the barrier did not reach the phase within the limit
+// Only the FIRST failure is kept (a producer that gives up makes the MMA issuer and the epilogue
+// give up later: their codes would hide the cause).
+__device__ __forceinline__ void record_error(int code) { atomicCAS(&g_linear_lif_error, 0, code); }
+// false if the barrier did not reach the phase within the limit, or if another role (of any CTA)
+// has already recorded a failure: dependent waits then return at once instead of running out
+// their own limit one after the other.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+    if (mbar_try_wait(bar, parity)) return true;
     const long long t0 = clock64();
-    while (!mbar_try_wait(bar, parity))
+    for (uint32_t spins = 1;; ++spins) {
+        if (mbar_try_wait(bar, parity)) return true;
         if (clock64() - t0 > kWaitCycles) return false;
-    return true;
+        if ((spins & 63u) == 0u && *reinterpret_cast<volatile int*>(&g_linear_lif_error) != 0) return false;
+    }
 }
 
 __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1) {
@@ -207,7 +202,7 @@ linear_lif_fwd_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
             for (int kb = 0; kb < num_kb; ++kb) {
                 const int s = kb % STAGES;
                 const uint32_t parity = ((kb / STAGES) & 1) ^ 1;     // first pass: slots start empty
-                if (!mbar_wait(&sm.empty[s], parity)) { atomicExch(&g_linear_lif_error, 1); break; }
+                if (!mbar_wait(&sm.empty[s], parity)) { record_error(1); break; }
                 mbar_expect_tx(&sm.full[s], kStageBytesA + kStageBytesB);
                 tma_load_2d(sm.a[s], &map_w, &sm.full[s], kb * BK, m0);
                 tma_load_3d(sm.b[s], &map_x, &sm.full[s], kb * BK, b0, 0);
@@ -221,7 +216,7 @@ linear_lif_fwd_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
             for (int kb = 0; kb < num_kb && ok; ++kb) {
                 const int s = kb % STAGES;
                 const uint32_t parity = (kb / STAGES) & 1;
-                if (!mbar_wait(&sm.full[s], parity)) { atomicExch(&g_linear_lif_error, 2); ok = false; break; }
+                if (!mbar_wait(&sm.full[s], parity)) { record_error(2); ok = false; break; }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint64_t da = umma_desc_sw128(sm.a[s]);
                 const uint64_t db = umma_desc_sw128(sm.b[s]);
@@ -237,7 +232,7 @@ linear_lif_fwd_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
     } else {
         // ------------------------------ epilogue: LIF over the tile ---------------
         bool ok = mbar_wait(&sm.accum_full, 0);
-        if (!ok) atomicExch(&g_linear_lif_error, 3);
+        if (!ok) record_error(3);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         if (ok) {
             const int m = m0 + warp * 32 + lane;                     // this thread's output neuron
@@ -284,7 +279,7 @@ linear_lif_fwd_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
 // fill the other one; the epilogue writes its bf16 currents / spikes into a shared-memory tile
 // laid out [t][b][m] and hands it to one 3-D TMA store per output instead of 2-byte stores.
 //
-// WN = accumulator columns per tile, 128 or 256. Measured with linear_lif_trace: a K stage (four
+// WN = accumulator columns per tile, 128 or 256. Measured with cycle-counter stamps at the MMA issuer: a K stage (four
 // tcgen05.mma 128 x WN x 16) takes ~535 cycles for WN = 256, i.e. ~95 % of the tensor pipe's
 // rate, and the same ~531 cycles for WN = 128 - half the flops. So the wide tile is used
 // whenever it does not cost a round of parallelism (see pick_kernel()).
@@ -454,7 +449,6 @@ linear_lif_fwd_persistent_kernel(const __grid_constant__ CUtensorMap map_w, cons
         (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    if (threadIdx.x == 0) SNN_TRACE(45);
     const int num_kb = K / BK;
     const int tiles_m = M / BM;
     const int num_tiles = tiles_m * (B / BT);
@@ -487,7 +481,6 @@ linear_lif_fwd_persistent_kernel(const __grid_constant__ CUtensorMap map_w, cons
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = sm.tmem_base;
-    if (threadIdx.x == 0) SNN_TRACE(46);
 
     if (warp == 4) {
         // ------------------------------ TMA producer ------------------------------
@@ -500,7 +493,7 @@ linear_lif_fwd_persistent_kernel(const __grid_constant__ CUtensorMap map_w, cons
                     if (it < preloaded) continue;             // requested before the set-up sync
                     const int s = it % PSTAGES;
                     const uint32_t parity = ((it / PSTAGES) & 1) ^ 1;
-                    if (!mbar_wait(&sm.empty[s], parity)) { atomicExch(&g_linear_lif_error, 1); ok = false; break; }
+                    if (!mbar_wait(&sm.empty[s], parity)) { record_error(1); ok = false; break; }
                     mbar_expect_tx(&sm.full[s], kStageBytesA + PersistentCfg<WN>::kStageBytesB);
                     tma_load_2d(sm.a[s], &map_w, &sm.full[s], kb * BK, m0);
                     tma_load_3d(sm.b[s], &map_x, &sm.full[s], kb * BK, b0, 0);
@@ -516,15 +509,14 @@ linear_lif_fwd_persistent_kernel(const __grid_constant__ CUtensorMap map_w, cons
             for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
                 const int buf = local & 1;
                 const uint32_t acc_parity = ((local >> 1) & 1) ^ 1;      // first use of a buffer passes
-                if (!mbar_wait(&sm.acc_empty[buf], acc_parity)) { atomicExch(&g_linear_lif_error, 4); break; }
+                if (!mbar_wait(&sm.acc_empty[buf], acc_parity)) { record_error(4); break; }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint32_t tmem_acc = tmem_base + buf * WN;
                 for (int kb = 0; kb < num_kb; ++kb, ++it) {
                     const int s = it % PSTAGES;
                     const uint32_t parity = (it / PSTAGES) & 1;
-                    if (!mbar_wait(&sm.full[s], parity)) { atomicExch(&g_linear_lif_error, 2); ok = false; break; }
+                    if (!mbar_wait(&sm.full[s], parity)) { record_error(2); ok = false; break; }
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                    if (it < 40) SNN_TRACE(it);
                     const uint64_t da = umma_desc_sw128(sm.a[s]);
                     const uint64_t db = umma_desc_sw128(sm.b[s]);
 #pragma unroll
@@ -533,7 +525,6 @@ linear_lif_fwd_persistent_kernel(const __grid_constant__ CUtensorMap map_w, cons
                     umma_commit(&sm.empty[s]);
                 }
                 if (ok) umma_commit(&sm.acc_full[buf]);
-                if (local == 0) SNN_TRACE(40);
             }
         }
     } else {
@@ -549,11 +540,10 @@ linear_lif_fwd_persistent_kernel(const __grid_constant__ CUtensorMap map_w, cons
             const uint32_t acc_parity = (local >> 1) & 1;
             if (elected) {
                 const bool ok0 = mbar_wait(&sm.acc_full[buf], acc_parity);
-                if (!ok0) atomicExch(&g_linear_lif_error, 3);
+                if (!ok0) record_error(3);
                 sm.epi_ok[g] = ok0 ? 1u : 0u;
             }
             group_barrier(g);
-            if (elected && local == 0) SNN_TRACE(42 + 10 * g);
             if (sm.epi_ok[g] == 0u) break;
             mbar_wait(&sm.acc_full[buf], acc_parity);     // already complete: returns at once, orders this thread
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -571,9 +561,7 @@ linear_lif_fwd_persistent_kernel(const __grid_constant__ CUtensorMap map_w, cons
         }
         // shared memory must outlive the reads of the last stores; the writes themselves complete
         // before the grid does
-        if (elected) SNN_TRACE(43 + 10 * g);
         if (elected) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
-        if (elected) SNN_TRACE(44 + 10 * g);
     }
 
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -686,7 +674,6 @@ linear_lif_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
         (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    if (threadIdx.x == 0) SNN_TRACE(45);
     const uint32_t rank = cluster_ctarank();
     const bool leader = rank == 0;
     const int pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
@@ -714,7 +701,6 @@ linear_lif_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
     cluster_sync_all();                         // the peer's barriers are initialised past this point
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = sm.tmem_base;
-    if (threadIdx.x == 0) SNN_TRACE(46);
 
     if (warp == 4) {
         // ------------------------------ TMA producer (both CTAs) ------------------
@@ -727,7 +713,7 @@ linear_lif_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
                 for (int kb = 0; kb < num_kb; ++kb, ++it) {
                     const int s = it % PAIR_STAGES;
                     const uint32_t parity = ((it / PAIR_STAGES) & 1) ^ 1;
-                    if (!mbar_wait(&sm.empty[s], parity)) { atomicExch(&g_linear_lif_error, 11); ok = false; break; }
+                    if (!mbar_wait(&sm.empty[s], parity)) { record_error(11); ok = false; break; }
                     const uint32_t full_leader = mapa_shared(smem_u32(&sm.full[s]), 0);
                     if (leader) mbar_expect_tx(&sm.full[s], 2 * (kStageBytesA + (PAIR_N / 2) * BK * 2));
                     tma_load_2d_pair(sm.a[s], &map_w, full_leader, kb * BK, m0);
@@ -744,15 +730,14 @@ linear_lif_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
             for (int tile = pair; tile < num_tiles && ok; tile += num_pairs, ++local) {
                 const int buf = local & 1;
                 const uint32_t acc_parity = ((local >> 1) & 1) ^ 1;      // first use of a buffer passes
-                if (!mbar_wait(&sm.acc_empty[buf], acc_parity)) { atomicExch(&g_linear_lif_error, 14); break; }
+                if (!mbar_wait(&sm.acc_empty[buf], acc_parity)) { record_error(14); break; }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint32_t tmem_acc = tmem_base + buf * PAIR_N;
                 for (int kb = 0; kb < num_kb; ++kb, ++it) {
                     const int s = it % PAIR_STAGES;
                     const uint32_t parity = (it / PAIR_STAGES) & 1;
-                    if (!mbar_wait(&sm.full[s], parity)) { atomicExch(&g_linear_lif_error, 12); ok = false; break; }
+                    if (!mbar_wait(&sm.full[s], parity)) { record_error(12); ok = false; break; }
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                    if (it < 40) SNN_TRACE(it);
                     const uint64_t da = umma_desc_sw128(sm.a[s]);
                     const uint64_t db = umma_desc_sw128(sm.b[s]);
 #pragma unroll
@@ -761,7 +746,6 @@ linear_lif_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
                     umma_commit_pair(&sm.empty[s]);
                 }
                 if (ok) umma_commit_pair(&sm.acc_full[buf]);
-                if (local == 0) SNN_TRACE(40);
             }
         }
     } else {
@@ -780,11 +764,10 @@ linear_lif_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
             const uint32_t acc_parity = (local >> 1) & 1;
             if (elected) {
                 const bool ok0 = mbar_wait(&sm.acc_full[buf], acc_parity);
-                if (!ok0) atomicExch(&g_linear_lif_error, 13);
+                if (!ok0) record_error(13);
                 sm.epi_ok[g] = ok0 ? 1u : 0u;
             }
             group_barrier(g);
-            if (elected && local == 0) SNN_TRACE(42 + 10 * g);
             if (sm.epi_ok[g] == 0u) break;
             mbar_wait(&sm.acc_full[buf], acc_parity);     // already complete: orders this thread
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -800,9 +783,7 @@ linear_lif_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
                 lif_epilogue_tile<T, PAIR_N, false>(sm.epi[g], staged, g, elected, lane_base, row, bias_m, alpha, thresh,
                                                     t_real, &map_spike, &map_current, write_current, m0, b0, drained);
         }
-        if (elected) SNN_TRACE(43 + 10 * g);
         if (elected) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
-        if (elected) SNN_TRACE(44 + 10 * g);
     }
 
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -1058,15 +1039,6 @@ int snn_linear_lif_fwd(const void* x, const void* weight, const float* bias, voi
         return launch_persistent<S, 128>(mw, mx, ms, mc, wc, bias, Bi, Ki, Mi, alpha, thresh, Ti, st);
     });
 }
-
-#ifdef SNN_LINEAR_LIF_TRACE
-// trace builds only: copies the stamps of the first `ctas` CTAs (kTraceSlots values each) to `out`
-int snn_linear_lif_trace_read(long long* out, int ctas) {
-    if (ctas < 0 || ctas > 1024) return SNN_ERR_SHAPE;
-    cudaError_t e = cudaMemcpyFromSymbol(out, g_linear_lif_trace, sizeof(long long) * kTraceSlots * ctas);
-    return e == cudaSuccess ? SNN_OK : SNN_ERR_CUDA;
-}
-#endif
 
 int snn_linear_lif_error(int reset) {
     int v = 0;

@@ -16,8 +16,14 @@ This wrapper keeps the numerics and does overlap:
   * a post-accumulate-grad hook counts arrivals; when a bucket is complete its all-reduce is
     issued on a side stream that waits only for the work recorded so far, so NCCL runs over
     NVLink while the remaining layers' BPTT kernels keep the SMs busy;
+  * buckets are always reduced in bucket order, every bucket exactly once per backward, so every
+    rank issues the same sequence of collectives whatever subset of its parameters received a
+    gradient (a bucket that completes early waits for the buckets before it; ``finish()`` reduces
+    what is left, untouched buckets included - their gradients are the zeros ``zero_grad()`` left).
+    apex's fallback has the same property: it always reduces the whole flat gradient set
+    (distributed.py:491-510). Ranks that issued different numbers of all-reduces would hang NCCL;
   * ``finish()`` (called automatically at the end of backward through an autograd engine
-    callback) makes the compute stream wait for the outstanding reductions.
+    callback) also makes the compute stream wait for the outstanding reductions.
 On CPU tensors (gloo) the same logic runs without streams.
 """
 import torch
@@ -34,7 +40,8 @@ class DistributedDataParallel(torch.nn.Module):
         self.params = [p for p in module.parameters() if p.requires_grad]
         self._broadcast_parameters()
         self._build_buckets(bucket_mb)
-        self._pending = []          # (bucket index, work handle or None)
+        self._pending = []          # indices of buckets whose reduction runs on the side stream
+        self._next_bucket = 0       # buckets [0, _next_bucket) have been reduced in this backward
         self._callback_queued = False
         self._comm_stream = None
         dev = self.params[0].device if self.params else torch.device("cpu")
@@ -91,6 +98,7 @@ class DistributedDataParallel(torch.nn.Module):
         for b in self.buckets:
             b["flat"].zero_()
             b["ready"] = 0
+        self._next_bucket = 0
 
     def _on_grad_ready(self, param):
         k = self._bucket_of[param]
@@ -104,8 +112,16 @@ class DistributedDataParallel(torch.nn.Module):
         if not self._callback_queued:
             torch.autograd.Variable._execution_engine.queue_callback(self.finish)
             self._callback_queued = True
-        if b["ready"] == len(b["params"]):
-            self._reduce_bucket(k)
+        self._reduce_complete_prefix()
+
+    def _reduce_complete_prefix(self):
+        """Issue, in bucket order, the reductions of the leading buckets that are complete."""
+        while self._next_bucket < len(self.buckets):
+            b = self.buckets[self._next_bucket]
+            if b["ready"] < len(b["params"]):
+                break
+            self._reduce_bucket(self._next_bucket)
+            self._next_bucket += 1
 
     def _offset_bytes(self, param, b):
         off = 0
@@ -141,11 +157,15 @@ class DistributedDataParallel(torch.nn.Module):
     def finish(self):
         """Join the side stream; gradients are averaged once work queued after this runs."""
         self._callback_queued = False
+        # whatever has not been reduced yet (a parameter, or a whole bucket, took no part in this
+        # backward on this rank): reduce it now, in order, so the collective sequence is the same
+        # on every rank
+        while self._next_bucket < len(self.buckets):
+            self._reduce_bucket(self._next_bucket)
+            self._next_bucket += 1
         for b in self.buckets:
-            if 0 < b["ready"] < len(b["params"]):
-                # a parameter did not take part in this backward: reduce what there is
-                self._reduce_bucket(self.buckets.index(b))
             b["ready"] = 0
+        self._next_bucket = 0
         if self._pending:
             flat = self.buckets[self._pending[0]]["flat"]
             torch.cuda.current_stream(flat.device).wait_stream(self._comm_stream)

@@ -279,10 +279,19 @@ conv_func = ConvFunc.apply
 # (reference snnlib_func.py:261-379). reduce_op = [ReduceOp enum, process group, world size].
 # ------------------------------------------------------------------------------------------
 def _allreduce_channel_sums(local_xhat, local_xhatx, reduce_op):
+    """Mean over ranks of the two per-channel vectors, as one [2, C] all-reduce (the reference
+    sends them as two messages, snnlib_func.py:278-279; the arithmetic is the same)."""
     op, group, world = reduce_op
-    torch.distributed.all_reduce(local_xhat, op.SUM, group)
-    torch.distributed.all_reduce(local_xhatx, op.SUM, group)
-    return local_xhat / world, local_xhatx / world
+    base = local_xhat._base
+    if (base is not None and base is local_xhatx._base and base.dim() == 2 and base.shape[0] == 2
+            and base.is_contiguous() and local_xhat.data_ptr() == base.data_ptr()
+            and local_xhatx.data_ptr() == base[1].data_ptr()):
+        both = base                      # the two rows of the buffer the means kernel wrote: no copy
+    else:
+        both = torch.stack((local_xhat, local_xhatx))
+    torch.distributed.all_reduce(both, op.SUM, group)
+    both /= world
+    return both[0], both[1]
 
 
 class BnDistFunc(torch.autograd.Function):

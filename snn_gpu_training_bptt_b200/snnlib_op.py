@@ -89,13 +89,19 @@ class _BnStats(nn.Module):
                 self.world_size = torch.distributed.get_world_size(self.process_group)
         if not self.train_bn:
             return self.running_var, self.running_mean
+        # Statistics are always fp32, whatever the activation dtype (the kernels take fp32
+        # var / mean beside bf16 / fp16 tensors; E[x^2] - E[x]^2 in 16 bits would be unusable).
+        low = x.dtype in (torch.bfloat16, torch.float16)
         if self._distributed:
-            mean = torch.mean(x, dim=self.dim_bn)
-            mean_sq = torch.mean(x * x, dim=self.dim_bn)
-            torch.distributed.all_reduce(mean, self.ReduceOp.SUM, self.process_group)
-            torch.distributed.all_reduce(mean_sq, self.ReduceOp.SUM, self.process_group)
-            mean = mean / self.world_size
-            var = mean_sq / self.world_size - mean ** 2
+            # one [2, C] message carries both moments (the reference sends two [C] messages,
+            # snnlib_op.py:268-269); same arithmetic: mean of the ranks' means and mean squares
+            moments = torch.stack((self._mean32(x), self._mean_sq32(x)))
+            torch.distributed.all_reduce(moments, self.ReduceOp.SUM, self.process_group)
+            mean = moments[0] / self.world_size
+            var = moments[1] / self.world_size - mean ** 2
+        elif low:
+            mean = self._mean32(x)
+            var = (self._mean_sq32(x) - mean ** 2).clamp_(min=0.0)
         else:
             var, mean = torch.var_mean(x, dim=self.dim_bn, unbiased=False)
         m = self._momentum
@@ -103,6 +109,17 @@ class _BnStats(nn.Module):
             self.running_var.mul_(1 - m).add_(var.detach() * (m * self.factor))
             self.running_mean.mul_(1 - m).add_(mean.detach() * m)
         return var, mean
+
+
+    def _mean32(self, x):
+        return torch.mean(x, dim=self.dim_bn, dtype=torch.float32)
+
+    def _mean_sq32(self, x):
+        """E[x^2] per channel, accumulated in fp32 without an fp32 copy of a 16-bit activation."""
+        if x.dtype == torch.float32:
+            return torch.mean(x * x, dim=self.dim_bn)
+        count = x.numel() / self._bn_channels
+        return torch.linalg.vector_norm(x, 2, dim=self.dim_bn, dtype=torch.float32).square_().div_(count)
 
 
 class Bn(_BnStats):

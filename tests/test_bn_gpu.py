@@ -3,8 +3,8 @@ split) against the CPU oracle and against vectors recorded from the reference's 
 
 Forward is compared exactly with the oracle (same operation order): ivar, membrane potentials
 and spikes bit-equal. Backward sums are accumulated with atomics in a different order than the
-oracle's serial loops, so gradients are held to 1e-4 of the gradient's scale (BASELINE's
-gradient bar); against the reference's gold modules the bars of tests/test_oracle_bn.py apply."""
+oracle's serial loops, so gradients are held to 1e-4 of the gradient's scale (the
+gradient bar this library is built to); against the reference's gold modules the bars of tests/test_oracle_bn.py apply."""
 import os
 import socket
 import subprocess

@@ -1,7 +1,7 @@
 """GPU parity of the CUDA LIF kernels (called through the C ABI) against the CPU oracle and
 the golden vectors generated from the reference's gold_op.py.
 
-Bars: membrane potentials and spikes bit-exact in fp32 (BASELINE allows 1e-5 relative and
+Bars: membrane potentials and spikes bit-exact in fp32 (the stated bar is 1e-5 relative and
 spike flips only where |u - thresh| < 1e-6; exact is stricter and is what the arithmetic
 gives); gradients exact in value in fp32, which is inside the 1e-4 relative bar.
 """

@@ -3,9 +3,10 @@
 Some hosts cannot call cudaMalloc where the backward pass runs (their own allocator owns the
 whole GPU, or the call sits in a latency-critical loop, or a plugin sandbox only passes buffers
 in and out). For them the library keeps the membrane scratch in an array compiled into it.
-This file checks, through the C ABI, that the entry point gives exactly what snn_lif_bwd gives,
-on two calls in a row that reuse the shared array with different problems, that it really
-leaves device memory alone, and that it refuses problems beyond the array's size.
+This file checks, through the C ABI, that the entry point gives exactly what snn_lif_bwd gives
+and what the CPU oracle gives, on two calls in a row that reuse the shared array with different
+problems, that it really leaves device memory alone, and that it refuses problems beyond the
+array's size.
 
 Collected last on purpose (file name), so a run that stops at the first failure has already
 run every other test. It also passes when run alone in a fresh process.
@@ -53,6 +54,15 @@ def _existing(L, x, g, code):
     return out
 
 
+def _oracle(x, g):
+    """The CPU oracle's gradient, computed in the state type (fp32, or fp64 for fp64 tensors) on the
+    exactly representable inputs and rounded to the tensors' element type, as the kernels do."""
+    from oracle import lif_oracle as orc
+    state = torch.float64 if x.dtype == torch.float64 else torch.float32
+    want = orc.c_lif_bwd(x.cpu().to(state).numpy(), g.cpu().to(state).numpy(), A, TH, BE, IV)
+    return torch.from_numpy(want).to(x.dtype)
+
+
 def _noalloc(L, x, g, code):
     T, N = x.shape
     out = torch.full_like(x, float("nan"))
@@ -74,6 +84,9 @@ def test_two_calls_in_a_row_match_the_existing_entry_point(L):
         got = _noalloc(L, x, g, code)
         torch.cuda.synchronize()
         assert torch.equal(got, want), (T, N, dtype)   # fp32 bar: exact (tolerance of the suite: 1e-4 rel)
+        # and against the CPU oracle: equal in value (the oracle may emit -0.0 where the kernel emits +0.0)
+        oracle = _oracle(x, g)
+        assert bool((got.cpu() == oracle).all()), (T, N, dtype, "oracle")
     # same problem twice in a row gives the same bytes
     x, g = _inputs(40, 100_000, 1, torch.float32)
     assert torch.equal(_noalloc(L, x, g, 0), _noalloc(L, x, g, 0))
@@ -107,7 +120,9 @@ def test_sizes_beyond_the_built_in_array_are_refused(L):
     # exactly at the limit is accepted
     T, N = 64, limit // 64
     xb, gb = _inputs(T, N, 5, torch.float32)
-    assert torch.equal(_noalloc(L, xb, gb, 0), _existing(L, xb, gb, 0))
+    got = _noalloc(L, xb, gb, 0)
+    assert torch.equal(got, _existing(L, xb, gb, 0))
+    assert bool((got.cpu() == _oracle(xb, gb)).all())
 
 
 def test_python_wrapper_requires_preallocated_output(L):
