@@ -213,8 +213,10 @@ int snn_channel_sum(const void *grad, float *out, int64_t outer, int64_t C, int6
  * rest of the tile empty), K % 64 == 0, M % 128 == 0; otherwise SNN_ERR_UNSUPPORTED (use
  * snn_lif_fwd after a library GEMM). Outputs that are not 16-byte aligned are accepted for
  * T = 4 and T = 8 only (SNN_ERR_ALIGN otherwise). Waits inside the kernel are bounded; snn_linear_lif_error() returns 0,
- * or the code of the wait that expired (1 producer, 2 MMA issuer, 3 epilogue) after synchronising
- * with the device, and clears it when `reset` is non-zero.
+ * or the code of the FIRST wait that expired (1 producer, 2 / 4 MMA issuer, 3 epilogue; 11-14 the
+ * same roles of the CTA-pair kernel) after synchronising with the device, and clears it when
+ * `reset` is non-zero. While the word is non-zero, waits of later launches give up early and
+ * their results are undefined: clear it before going on.
  * -------------------------------------------------------------------------------------- */
 int snn_linear_lif_fwd_supported(int64_t T, int64_t B, int64_t K, int64_t M, int dtype);
 /* Which kernel snn_linear_lif_fwd runs for this problem on a device with `sm_count` SMs (no GPU
@@ -227,6 +229,35 @@ int snn_linear_lif_fwd(const void *x, const void *weight, const float *bias, voi
                        void *spike, int64_t T, int64_t B, int64_t K, int64_t M, int dtype,
                        float alpha, float thresh, void *stream);
 int snn_linear_lif_error(int reset);
+
+/*
+ * Backward through time of the fused synaptic linear + LIF layer on the tcgen05 tensor cores:
+ *   dU = LIF reverse pass of (current, grad_spike)   (same arithmetic as snn_lif_bwd, bf16 I/O)
+ *   grad_x[t, b, :] = dU[t, b, :] @ weight ;  grad_weight = sum_(t,b) dU[t,b,:]^T x[t,b,:] ;
+ *   grad_bias = sum_(t,b) dU[t,b,:]
+ * Replaces fire_bp followed by fc_bp of the reference (snnlib/cuda/snn.cpp:270-279 ->
+ * snn_kernel_bp.cu:141-168, and snn.cpp:594-602 -> fc_bp_cuda, snn_kernel_bp.cu:1131-1173: 2*T
+ * at::mm calls plus at::sum). Two launches: one kernel writes dU (bf16) and per-block partial
+ * bias sums into the workspace; one persistent tcgen05 kernel computes both gradient GEMMs,
+ * reading weight, x and dU in place (no transposed copies) and summing the bias partials in a
+ * fixed order (results are reproducible run to run).
+ *   x [T, B, K] bf16, weight [M, K] bf16, current / grad_spike [T, B, M] bf16 (current is the
+ *   LIF input that snn_linear_lif_fwd wrote), all 16-byte aligned;
+ *   grad_x [T, B, K] bf16 or NULL (skipped); grad_weight [M, K] of grad_weight_dtype (SNN_BF16 or
+ *   SNN_F32) or NULL (skipped); grad_bias [M] fp32 or NULL (needs grad_weight);
+ *   workspace: snn_linear_lif_bwd_workspace_bytes() bytes of device scratch, 256-byte aligned.
+ * Supported when snn_linear_lif_bwd_supported() returns 1: SNN_BF16, 1 <= T <= 16, T*B >= 128,
+ * K >= 64, M >= 128, K % 8 == 0, M % 8 == 0; otherwise SNN_ERR_UNSUPPORTED (use snn_lif_bwd and
+ * library GEMMs). Bounded waits report through snn_linear_lif_error() with codes 21 (producer),
+ * 22 / 24 (MMA issuer), 23 (epilogue).
+ */
+int snn_linear_lif_bwd_supported(int64_t T, int64_t B, int64_t K, int64_t M, int dtype);
+int64_t snn_linear_lif_bwd_workspace_bytes(int64_t T, int64_t B, int64_t K, int64_t M, int dtype);
+int snn_linear_lif_bwd(const void *x, const void *weight, const void *current,
+                       const void *grad_spike, void *grad_x, void *grad_weight, float *grad_bias,
+                       int64_t T, int64_t B, int64_t K, int64_t M, int dtype,
+                       int grad_weight_dtype, float alpha, float thresh, float beta, float interval,
+                       void *workspace, size_t workspace_bytes, void *stream);
 
 /*
  * LIF backward through time for callers that may not allocate device memory.

@@ -34,6 +34,10 @@ SIGNATURES = {
     "snn_linear_lif_fwd_plan": (_int, [_i64, _i64, _i64, _i64, _int, _int]),
     "snn_linear_lif_fwd": (_int, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _int, _f32, _f32, _vp]),
     "snn_linear_lif_error": (_int, [_int]),
+    "snn_linear_lif_bwd_supported": (_int, [_i64, _i64, _i64, _i64, _int]),
+    "snn_linear_lif_bwd_workspace_bytes": (_i64, [_i64, _i64, _i64, _i64, _int]),
+    "snn_linear_lif_bwd": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _int, _int,
+                                  _f32, _f32, _f32, _f32, _vp, _sz, _vp]),
     "snn_channel_bias_add": (_int, [_vp, _vp, _i64, _i64, _i64, _int, _vp]),
     "snn_channel_sum": (_int, [_vp, _vp, _i64, _i64, _i64, _int, _vp]),
     "snn_bn_lif_fwd": (_int, [_vp, _vp, _vp, _vp, _vp, _f32, _vp, _vp, _vp, _i64, _i64, _i64, _i64,
@@ -435,6 +439,8 @@ def linear_lif_fwd(x, weight, bias, alpha, thresh, want_current=True):
     b = bias.float().contiguous() if bias is not None else None
     T, B, K = x.shape
     M = w.shape[0]
+    if b is not None and b.numel() != M:
+        raise ValueError("linear_lif_fwd: bias must have one entry per output neuron")
     with torch.cuda.device(x.device):
         spike = torch.empty((T, B, M), dtype=torch.bfloat16, device=x.device)
         current = torch.empty_like(spike) if want_current else None
@@ -442,6 +448,50 @@ def linear_lif_fwd(x, weight, bias, alpha, thresh, want_current=True):
                                       DTYPE_CODE[x.dtype], float(alpha), float(thresh), _stream(x.device))
     check("snn_linear_lif_fwd", rc)
     return current, spike
+
+
+def linear_lif_bwd_supported(x, weight):
+    """True if the tcgen05 backward covers this problem (bf16 x, T <= 16, T*B >= 128, K >= 64, M >= 128)."""
+    if x.dim() != 3 or weight.dim() != 2 or x.dtype != torch.bfloat16 or not x.is_cuda:
+        return False
+    T, B, K = x.shape
+    return bool(lib().snn_linear_lif_bwd_supported(T, B, K, weight.shape[0], DTYPE_CODE[x.dtype]))
+
+
+def linear_lif_bwd(x, weight, current, grad_spike, alpha, thresh, beta, interval, need_grad_x=True,
+                   need_grad_weight=True, need_grad_bias=True, grad_weight_dtype=torch.float32):
+    """(grad_x, grad_weight, grad_bias) of ``LIF(x @ weight^T + bias)`` from the saved LIF input
+    ``current`` and the upstream ``grad_spike``: the LIF reverse pass and both gradient GEMMs on the
+    library's own kernels (snn_linear_lif_bwd). x [T, B, K], current / grad_spike [T, B, M] and
+    weight [M, K] in bf16; grad_weight comes out in ``grad_weight_dtype`` (fp32 or bf16), grad_bias
+    in fp32. Entries that are not needed are None."""
+    if not linear_lif_bwd_supported(x, weight):
+        raise ValueError("linear_lif_bwd: unsupported problem (needs bf16, T <= 16, T*B >= 128, K >= 64, "
+                         "M >= 128, K % 8 == 0, M % 8 == 0)")
+    if weight.dtype != torch.bfloat16 or current.dtype != torch.bfloat16:
+        raise TypeError("linear_lif_bwd: weight and current must be bfloat16")
+    if grad_weight_dtype not in (torch.float32, torch.bfloat16):
+        raise TypeError("linear_lif_bwd: grad_weight_dtype must be float32 or bfloat16")
+    x, weight, current = x.contiguous(), weight.contiguous(), current.contiguous()
+    grad_spike = grad_spike.to(torch.bfloat16).contiguous()
+    T, B, K = x.shape
+    M = weight.shape[0]
+    if current.shape != (T, B, M) or grad_spike.shape != (T, B, M) or weight.shape[1] != K:
+        raise ValueError("linear_lif_bwd: shape mismatch")
+    need_grad_weight = need_grad_weight or need_grad_bias
+    L = lib()
+    with torch.cuda.device(x.device):
+        need = L.snn_linear_lif_bwd_workspace_bytes(T, B, K, M, DTYPE_CODE[x.dtype])
+        ws = torch.empty(need, dtype=torch.uint8, device=x.device)
+        gx = torch.empty_like(x) if need_grad_x else None
+        gw = torch.empty((M, K), dtype=grad_weight_dtype, device=x.device) if need_grad_weight else None
+        gb = torch.empty(M, dtype=torch.float32, device=x.device) if need_grad_bias else None
+        rc = L.snn_linear_lif_bwd(_ptr(x), _ptr(weight), _ptr(current), _ptr(grad_spike), _ptr(gx), _ptr(gw),
+                                  _ptr(gb), T, B, K, M, DTYPE_CODE[x.dtype], DTYPE_CODE[grad_weight_dtype],
+                                  float(alpha), float(thresh), float(beta), float(interval), _ptr(ws), need,
+                                  _stream(x.device))
+    check("snn_linear_lif_bwd", rc)
+    return gx, gw, gb
 
 
 def linear_lif_error(reset=True):

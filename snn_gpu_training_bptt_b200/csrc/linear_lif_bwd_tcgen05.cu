@@ -1,0 +1,574 @@
+// Backward through time of the fused synaptic linear + LIF layer on the tcgen05 tensor cores.
+//
+//   dU[t, b, :]   = LIF reverse pass over t of (current, grad_spike)        (fp32 state, bf16 I/O)
+//   grad_x[t,b,:] = dU[t, b, :] @ W                                         (bf16 operands, fp32 accumulation)
+//   grad_W        = sum over (t, b) of dU[t, b, :]^T x[t, b, :]
+//   grad_b        = sum over (t, b) of dU[t, b, :]
+//
+// In the reference this is fire_bp (snnlib/cuda/snn_kernel_bp.cu:141-168: membrane rebuild +
+// fire_bp_kernel :95-139) followed by fc_bp_cuda (:1131-1173): per time step one at::mm for the
+// input gradient and one for the weight gradient, accumulated over t, plus at::sum for the bias
+// (fire_fc_bp_cuda :1065-1128 is the same pair in the other order). Here:
+//
+//   1. lif_du_kernel      one pass over current / grad_spike (both bf16, written by the forward
+//                         kernel / the layer above): rebuilds u_t in registers, walks time in
+//                         reverse, writes dU in bf16 (the GEMM operand) and per-block column sums
+//                         of it (fp32 partials of grad_b, fixed summation order).
+//   2. bwd_gemm_kernel    ONE persistent launch that walks the tiles of both gradient GEMMs:
+//                         D[i, j] = sum_r A(i, r) * B(j, r), 128 x 256 tiles, 64 reduction indices
+//                         per pipeline stage, two accumulators in tensor memory so the epilogue
+//                         of a tile overlaps the MMAs of the next.
+//                           grad_x: i = (t,b), j = k, r = m:  A = dU [TB][M]   (K-major),
+//                                                             B = W  [M][K]    (MN-major)
+//                           grad_W: i = m, j = k, r = (t,b):  A = dU [TB][M]   (MN-major),
+//                                                             B = x  [TB][K]   (MN-major)
+//                         MN-major operands are read by the tensor core straight from the
+//                         row-major tensors (TMA boxes of 64 reduction rows x 64 elements, see
+//                         umma_desc_sw128_mn): no transposed copy of W, x or dU is ever made.
+//                         The epilogue converts the accumulator to the output type, stages
+//                         128-byte rows in swizzled shared memory (16-byte stores, conflict-free)
+//                         and writes them with 2-D TMA stores. The CTA that owns the first tile
+//                         of a grad_W row block also adds up that block's bias partials.
+//
+// Roles per CTA as in the forward kernel: warp 4 = TMA producer (one lane), warp 5 = MMA issuer
+// and TMEM owner, warps 0-3 and 6-9 = two epilogue groups that split a tile's columns. All
+// mbarrier waits are bounded (~1 s) and report through an error word. Tiles that reach past the
+// end of a tensor are handled by TMA itself (loads fill zeros, stores clip).
+#include "../../include/snn_b200.h"
+#include "lif_kernels.cuh"
+#include "tcgen05_common.cuh"
+
+namespace snn_internal {
+void set_last_cuda_error(int e);     // defined in lif_capi.cu
+int linear_lif_bwd_error(int reset);   // defined below; read by snn_linear_lif_error()
+}
+
+namespace {
+
+using namespace snn_tc;
+
+// ---------------------------------------------------------------------------------------------
+// 1. dU = LIF reverse pass, bf16 in / bf16 out, plus column sums
+// ---------------------------------------------------------------------------------------------
+// Block = 128 output neurons (128/VEC threads of VEC consecutive neurons) x RB batch items; every
+// thread keeps all T steps of its VEC neurons in registers (same arithmetic as lif_bwd_kernel:
+// products and sums rounded one by one). partials[blockIdx.y][m] = sum over the block's batch
+// items and all t of the bf16-rounded dU, i.e. exactly what the weight-gradient GEMM sees.
+template <int TMAX, int VEC, bool EXACT>
+__device__ __forceinline__ void lif_du_body(const __nv_bfloat16* __restrict__ cur,
+                                            const __nv_bfloat16* __restrict__ gs,
+                                            __nv_bfloat16* __restrict__ du, float* __restrict__ partials,
+                                            int T, int B, int M, float alpha, float thresh, float beta,
+                                            float interval)
+{
+    using namespace snn;
+    using IO = __nv_bfloat16;
+    constexpr int TX = 128 / VEC;          // threads along the neuron axis
+    constexpr int RB = 256 / TX;           // batch items per block
+    __shared__ float red[RB][128 + 4];
+
+    const int tx = threadIdx.x % TX, ty = threadIdx.x / TX;
+    const int m = blockIdx.x * 128 + tx * VEC;
+    const int b = blockIdx.y * RB + ty;
+    float colsum[VEC];
+#pragma unroll
+    for (int v = 0; v < VEC; ++v) colsum[v] = 0.f;
+
+    if (b < B && m < M) {
+        const long long N = static_cast<long long>(B) * M;
+        const long long i = static_cast<long long>(b) * M + m;
+        Pack<IO, VEC> xin[TMAX], gin[TMAX];
+#pragma unroll
+        for (int t = 0; t < TMAX; ++t)
+            if (EXACT || t < T) xin[t] = ld_stream<IO, VEC>(cur + static_cast<long long>(t) * N + i);
+#pragma unroll
+        for (int t = 0; t < TMAX; ++t)
+            if (EXACT || t < T) gin[t] = ld_stream<IO, VEC>(gs + static_cast<long long>(t) * N + i);
+
+        float u[TMAX][VEC];
+        {
+            float uu[VEC], gate[VEC];
+#pragma unroll
+            for (int v = 0; v < VEC; ++v) { uu[v] = 0.f; gate[v] = 1.f; }
+#pragma unroll
+            for (int t = 0; t < TMAX; ++t) {
+                if (EXACT || t < T) {
+#pragma unroll
+                    for (int v = 0; v < VEC; ++v) {
+                        const float leak = mul_rn(mul_rn(alpha, uu[v]), gate[v]);
+                        uu[v] = add_rn(leak, Elem<IO>::load(xin[t].v[v]));
+                        gate[v] = (uu[v] > thresh) ? 0.f : 1.f;
+                        u[t][v] = uu[v];
+                    }
+                }
+            }
+        }
+        float gu[VEC];
+#pragma unroll
+        for (int v = 0; v < VEC; ++v) gu[v] = 0.f;
+#pragma unroll
+        for (int t = TMAX - 1; t >= 0; --t) {
+            if (EXACT || t < T) {
+                Pack<IO, VEC> out;
+#pragma unroll
+                for (int v = 0; v < VEC; ++v) {
+                    const float ut = u[t][v];
+                    const float ga = mul_rn(gu[v], alpha);
+                    float g = 0.f;
+                    if (inside_window(ut, thresh, interval)) g = sub_rn(Elem<IO>::load(gin[t].v[v]), mul_rn(ga, ut));
+                    const float keep = (ut <= thresh) ? 1.f : 0.f;
+                    gu[v] = add_rn(mul_rn(g, beta), mul_rn(ga, keep));
+                    out.v[v] = Elem<IO>::store(gu[v]);
+                    colsum[v] += Elem<IO>::load(out.v[v]);
+                }
+                st_stream<IO, VEC>(du + static_cast<long long>(t) * N + i, out);
+            }
+        }
+    }
+    if (partials == nullptr) return;
+#pragma unroll
+    for (int v = 0; v < VEC; ++v) red[ty][tx * VEC + v] = colsum[v];
+    __syncthreads();
+    if (threadIdx.x < 128) {
+        float s = 0.f;
+#pragma unroll
+        for (int r = 0; r < RB; ++r) s += red[r][threadIdx.x];
+        const int mm = blockIdx.x * 128 + threadIdx.x;
+        if (mm < M) partials[static_cast<long long>(blockIdx.y) * M + mm] = s;
+    }
+}
+
+template <int TMAX, int VEC>
+__global__ void __launch_bounds__(256)
+lif_du_kernel(const __nv_bfloat16* __restrict__ cur, const __nv_bfloat16* __restrict__ gs,
+              __nv_bfloat16* __restrict__ du, float* __restrict__ partials, int T, int B, int M, float alpha,
+              float thresh, float beta, float interval)
+{
+    if (T == TMAX) lif_du_body<TMAX, VEC, true>(cur, gs, du, partials, T, B, M, alpha, thresh, beta, interval);
+    else lif_du_body<TMAX, VEC, false>(cur, gs, du, partials, T, B, M, alpha, thresh, beta, interval);
+}
+
+constexpr int du_vec(int tmax) { return tmax <= 8 ? 8 : 4; }
+constexpr int du_rows_per_block(int tmax) { return 256 / (128 / du_vec(tmax)); }
+int du_tmax(int64_t T) { return T <= 2 ? 2 : (T <= 4 ? 4 : (T <= 8 ? 8 : 16)); }
+
+// ---------------------------------------------------------------------------------------------
+// 2. the two gradient GEMMs as one persistent kernel
+// ---------------------------------------------------------------------------------------------
+constexpr int TI = 128;              // tile rows    (i = TMEM lanes)
+constexpr int TJ = 256;              // tile columns (j = TMEM columns)
+constexpr int BR = 64;               // reduction indices per pipeline stage
+constexpr int UMMA_K = 16;
+constexpr int GSTAGES = 3;
+constexpr int kThreadsG = 320;
+constexpr uint32_t kBoxBytes = 64 * 64 * 2;                 // one 64 x 64 bf16 box
+constexpr uint32_t kStageA = TI * BR * 2;                   // 16 KB
+constexpr uint32_t kStageB = TJ * BR * 2;                   // 32 KB
+constexpr uint32_t kTmemColsG = 2 * TJ;                     // two accumulators = all of tensor memory
+constexpr uint32_t kUnitBytes = TI * 128;                   // one staged output unit: 128 rows of 128 bytes
+
+struct GemmProblem {
+    CUtensorMap map_a;               // A operand (see a_mn)
+    CUtensorMap map_b;               // B operand, always MN-major: boxes {64 j, 64 r}
+    CUtensorMap map_d;               // output [I][J], boxes {128 bytes of j, 128 i}, 128-byte swizzle
+    int a_mn;                        // 1: A is MN-major, boxes {64 i, 64 r}; 0: K-major, one box {64 r, 128 i}
+    int out_f32;                     // output element type: 1 fp32 (32 columns per unit), 0 bf16 (64)
+    int tiles_i, tiles_j, num_rb;    // tile grid and number of reduction stages
+    int tile_begin;                  // first tile of this problem in the kernel's tile list
+    int rows;                        // I
+    const float* bias_partials;      // [partial_rows][rows] or null
+    float* grad_bias;                // [rows] or null
+    int partial_rows;
+};
+struct GemmParams {
+    GemmProblem p[2];
+    int count;
+    int total_tiles;
+};
+
+struct __align__(1024) GemmStorage {
+    __nv_bfloat16 a[GSTAGES][TI * BR];
+    __nv_bfloat16 b[GSTAGES][TJ * BR];
+    unsigned char out[2][2][kUnitBytes];         // [epilogue group][double buffer]
+    uint64_t full[GSTAGES];
+    uint64_t empty[GSTAGES];
+    uint64_t acc_full[2];
+    uint64_t acc_empty[2];
+    uint32_t tmem_base;
+    uint32_t epi_ok[2];
+};
+
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t* r) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr));
+}
+
+__device__ __forceinline__ uint32_t pack_bf16x2(uint32_t lo_bits, uint32_t hi_bits) {
+    const __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(lo_bits), __uint_as_float(hi_bits));
+    return *reinterpret_cast<const uint32_t*>(&h);
+}
+
+// which problem a tile of the kernel's list belongs to
+__device__ __forceinline__ int problem_of(const GemmParams& P, int tile) {
+    return (P.count > 1 && tile >= P.p[1].tile_begin) ? 1 : 0;
+}
+
+// Epilogue of one accumulator for epilogue group g: the thread owns TMEM lane `row` = output row
+// i0 + row. The tile's 256 columns are cut into units of 128 output bytes per row (32 fp32 or 64
+// bf16 columns); group g takes units g, g + 2, ... Each unit is staged in one of the group's two
+// buffers as rows of 128 bytes whose 16-byte chunks are XOR-swizzled with (row & 7) - the layout
+// a 128-byte-swizzle tensor map expects - so the eight lanes that write chunk c of eight
+// consecutive rows hit eight different bank groups.
+template <bool F32, typename Drained>
+__device__ __forceinline__ void gemm_epilogue_tile(unsigned char (&stage)[2][kUnitBytes], int& k, int g, bool elected,
+                                                   uint32_t lane_base, int row, const CUtensorMap* map_d, int i0,
+                                                   int j0, Drained&& drained)
+{
+    constexpr int UC = F32 ? 32 : 64;           // columns per unit
+    constexpr int PER_GROUP = TJ / UC / 2;
+#pragma unroll 1
+    for (int u = 0; u < PER_GROUP; ++u) {
+        const int q = g + 2 * u;
+        uint32_t r[UC / 32][32];
+        tmem_ld32(lane_base + q * UC, r[0]);
+        if (!F32) tmem_ld32(lane_base + q * UC + 32, r[UC / 32 - 1]);
+        // the registers pass through the wait statement so that no use of them is scheduled ahead of it
+        tmem_ld_wait32(r[0]);
+        if (!F32) tmem_ld_wait32(r[UC / 32 - 1]);
+        if (u + 1 == PER_GROUP) {
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            drained();                          // last TMEM read of this tile done: give the buffer back
+        }
+        unsigned char* st = stage[k & 1];
+        uint4* rowp = reinterpret_cast<uint4*>(st + row * 128);
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+            uint4 v;
+            if (F32) {
+                v = make_uint4(r[0][4 * c], r[0][4 * c + 1], r[0][4 * c + 2], r[0][4 * c + 3]);
+            } else {
+                const uint32_t* h = r[c >> 2] + 8 * (c & 3);      // columns 8c .. 8c+7 of the unit
+                v = make_uint4(pack_bf16x2(h[0], h[1]), pack_bf16x2(h[2], h[3]), pack_bf16x2(h[4], h[5]),
+                               pack_bf16x2(h[6], h[7]));
+            }
+            rowp[c ^ (row & 7)] = v;
+        }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        // the other buffer's store (issued one unit ago) must have been read out of shared memory
+        // before anybody passes the barrier and starts writing the next unit into it
+        if (elected) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+        group_barrier(g);
+        if (elected) {
+            tma_store_2d(map_d, st, j0 + q * UC, i0);
+            asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+        }
+        ++k;
+    }
+}
+
+__global__ void __launch_bounds__(kThreadsG, 1)
+bwd_gemm_kernel(const __grid_constant__ GemmParams P)
+{
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
+    GemmStorage& sm = *reinterpret_cast<GemmStorage*>(
+        (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    if (threadIdx.x == 4 * 32) {
+        for (int s = 0; s < GSTAGES; ++s) { mbar_init(&sm.full[s], 1); mbar_init(&sm.empty[s], 1); }
+        for (int i = 0; i < 2; ++i) { mbar_init(&sm.acc_full[i], 1); mbar_init(&sm.acc_empty[i], 256); }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        for (int k = 0; k < P.count; ++k) {
+            asm volatile("prefetch.tensormap [%0];" ::"l"(&P.p[k].map_a) : "memory");
+            asm volatile("prefetch.tensormap [%0];" ::"l"(&P.p[k].map_b) : "memory");
+            asm volatile("prefetch.tensormap [%0];" ::"l"(&P.p[k].map_d) : "memory");
+        }
+    }
+    if (warp == 5) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sm.tmem_base)),
+                     "r"(kTmemColsG)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = sm.tmem_base;
+
+    if (warp == 4) {
+        // ------------------------------ TMA producer ------------------------------
+        if (lane == 0) {
+            int it = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < P.total_tiles && ok; tile += gridDim.x) {
+                const GemmProblem& pr = P.p[problem_of(P, tile)];
+                const int local = tile - pr.tile_begin;
+                const int i0 = (local % pr.tiles_i) * TI, j0 = (local / pr.tiles_i) * TJ;
+                for (int rb = 0; rb < pr.num_rb; ++rb, ++it) {
+                    const int s = it % GSTAGES;
+                    const uint32_t parity = ((it / GSTAGES) & 1) ^ 1;      // first pass: slots start empty
+                    if (!mbar_wait(&sm.empty[s], parity)) { record_error(21); ok = false; break; }
+                    mbar_expect_tx(&sm.full[s], kStageA + kStageB);
+                    const int r0 = rb * BR;
+                    unsigned char* a = reinterpret_cast<unsigned char*>(sm.a[s]);
+                    unsigned char* b = reinterpret_cast<unsigned char*>(sm.b[s]);
+                    if (pr.a_mn) {
+                        tma_load_2d(a, &pr.map_a, &sm.full[s], i0, r0);
+                        tma_load_2d(a + kBoxBytes, &pr.map_a, &sm.full[s], i0 + 64, r0);
+                    } else {
+                        tma_load_2d(a, &pr.map_a, &sm.full[s], r0, i0);
+                    }
+#pragma unroll
+                    for (int q = 0; q < TJ / 64; ++q)
+                        tma_load_2d(b + q * kBoxBytes, &pr.map_b, &sm.full[s], j0 + 64 * q, r0);
+                }
+            }
+        }
+    } else if (warp == 5) {
+        // ------------------------------ MMA issuer --------------------------------
+        if (lane == 0) {
+            int it = 0, local = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < P.total_tiles && ok; tile += gridDim.x, ++local) {
+                const GemmProblem& pr = P.p[problem_of(P, tile)];
+                const bool a_mn = pr.a_mn != 0;
+                const uint32_t idesc = a_mn ? umma_idesc_bf16(TI, TJ, true, true) : umma_idesc_bf16(TI, TJ, false, true);
+                // per 16 reduction indices: a K-major tile advances 32 bytes inside its 128-byte rows,
+                // an MN-major tile advances 16 rows of 128 bytes (descriptor address unit = 16 bytes)
+                const uint32_t a_step = a_mn ? (16 * 128) >> 4 : 32 >> 4;
+                constexpr uint32_t b_step = (16 * 128) >> 4;
+                const int buf = local & 1;
+                const uint32_t acc_parity = ((local >> 1) & 1) ^ 1;        // first use of a buffer passes
+                if (!mbar_wait(&sm.acc_empty[buf], acc_parity)) { record_error(24); break; }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t tmem_acc = tmem_base + buf * TJ;
+                for (int rb = 0; rb < pr.num_rb; ++rb, ++it) {
+                    const int s = it % GSTAGES;
+                    const uint32_t parity = (it / GSTAGES) & 1;
+                    if (!mbar_wait(&sm.full[s], parity)) { record_error(22); ok = false; break; }
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const uint64_t da = a_mn ? umma_desc_sw128_mn(sm.a[s], kBoxBytes) : umma_desc_sw128(sm.a[s]);
+                    const uint64_t db = umma_desc_sw128_mn(sm.b[s], kBoxBytes);
+#pragma unroll
+                    for (int k = 0; k < BR / UMMA_K; ++k)
+                        umma_bf16(tmem_acc, da + a_step * k, db + b_step * k, idesc, (rb | k) != 0 ? 1u : 0u);
+                    umma_commit(&sm.empty[s]);        // stage reusable once these MMAs have read it
+                }
+                if (ok) umma_commit(&sm.acc_full[buf]);
+            }
+        }
+    } else {
+        // ------------------------------ epilogue groups (warps 0-3, 6-9) ----------
+        const int g = warp >= 6 ? 1 : 0;
+        const int quarter = warp & 3;                     // the TMEM lanes this warp may touch
+        const int row = quarter * 32 + lane;
+        const bool elected = lane == 0 && warp == (g ? 6 : 0);
+        int local = 0, staged = 0;
+        for (int tile = blockIdx.x; tile < P.total_tiles; tile += gridDim.x, ++local) {
+            const GemmProblem& pr = P.p[problem_of(P, tile)];
+            const int tl = tile - pr.tile_begin;
+            const int i0 = (tl % pr.tiles_i) * TI, j0 = (tl / pr.tiles_i) * TJ;
+            // bias gradient of this row block: fixed-order sum of the dU kernel's partials, done
+            // by group 0 of the CTA that owns the block's first tile while the MMAs run
+            if (g == 0 && j0 == 0 && pr.grad_bias != nullptr && i0 + row < pr.rows) {
+                float s = 0.f;
+                for (int pz = 0; pz < pr.partial_rows; ++pz)
+                    s += pr.bias_partials[static_cast<long long>(pz) * pr.rows + i0 + row];
+                pr.grad_bias[i0 + row] = s;
+            }
+            const int buf = local & 1;
+            const uint32_t acc_parity = (local >> 1) & 1;
+            if (elected) {
+                const bool ok0 = mbar_wait(&sm.acc_full[buf], acc_parity);
+                if (!ok0) record_error(23);
+                sm.epi_ok[g] = ok0 ? 1u : 0u;
+            }
+            group_barrier(g);
+            if (sm.epi_ok[g] == 0u) break;
+            mbar_wait(&sm.acc_full[buf], acc_parity);     // already complete: returns at once, orders this thread
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+
+            const uint32_t lane_base = tmem_base + buf * TJ + (static_cast<uint32_t>(quarter * 32) << 16);
+            uint64_t* drained_bar = &sm.acc_empty[buf];
+            auto drained = [drained_bar] { mbar_arrive(drained_bar); };
+            if (pr.out_f32)
+                gemm_epilogue_tile<true>(sm.out[g], staged, g, elected, lane_base, row, &pr.map_d, i0, j0, drained);
+            else
+                gemm_epilogue_tile<false>(sm.out[g], staged, g, elected, lane_base, row, &pr.map_d, i0, j0, drained);
+        }
+        // shared memory must outlive the reads of the last stores
+        if (elected) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+    }
+
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 5) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemColsG)
+                     : "memory");
+    }
+}
+
+// ---- host side ---------------------------------------------------------------------------------
+inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+struct Workspace {
+    size_t du_bytes, partial_bytes, total;
+    int partial_rows;
+};
+Workspace workspace_layout(int64_t T, int64_t B, int64_t M) {
+    Workspace w;
+    const int rb = du_tmax(T) <= 8 ? du_rows_per_block(8) : du_rows_per_block(16);
+    w.partial_rows = static_cast<int>((B + rb - 1) / rb);
+    w.du_bytes = align_up(static_cast<size_t>(T) * B * M * 2, 256);
+    w.partial_bytes = align_up(static_cast<size_t>(w.partial_rows) * M * 4, 256);
+    w.total = w.du_bytes + w.partial_bytes;
+    return w;
+}
+
+template <int TMAX>
+void launch_du(const void* cur, const void* gs, void* du, float* partials, int T, int B, int M, float alpha,
+               float thresh, float beta, float interval, cudaStream_t st) {
+    constexpr int VEC = du_vec(TMAX);
+    constexpr int RB = du_rows_per_block(TMAX);
+    dim3 grid((M + 127) / 128, (B + RB - 1) / RB);
+    lif_du_kernel<TMAX, VEC><<<grid, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(cur),
+                                                   static_cast<const __nv_bfloat16*>(gs),
+                                                   static_cast<__nv_bfloat16*>(du), partials, T, B, M, alpha, thresh,
+                                                   beta, interval);
+}
+
+bool map2d(CUtensorMap* out, const void* base, int64_t inner, int64_t outer, uint32_t box_inner, uint32_t box_outer,
+           bool f32 = false) {
+    const cuuint64_t dims[2] = {static_cast<cuuint64_t>(inner), static_cast<cuuint64_t>(outer)};
+    const cuuint64_t strides[1] = {static_cast<cuuint64_t>(inner) * (f32 ? 4 : 2)};
+    const cuuint32_t box[2] = {box_inner, box_outer};
+    return cached_map(out, base, 2, dims, strides, box, true, f32);
+}
+
+}  // namespace
+
+namespace snn_internal {
+int linear_lif_bwd_error(int reset) {
+    int v = 0;
+    cudaError_t e = cudaMemcpyFromSymbol(&v, snn_tc::g_tc_error, sizeof(int));
+    if (e != cudaSuccess) { set_last_cuda_error(static_cast<int>(e)); return -1; }
+    if (reset && v != 0) {
+        const int zero = 0;
+        cudaMemcpyToSymbol(snn_tc::g_tc_error, &zero, sizeof(int));
+    }
+    return v;
+}
+}  // namespace snn_internal
+
+extern "C" {
+
+int snn_linear_lif_bwd_supported(int64_t T, int64_t B, int64_t K, int64_t M, int dtype) {
+    if (dtype != SNN_BF16) return 0;
+    if (T < 1 || T > 16 || B < 1) return 0;
+    // TMA: row pitches are multiples of 16 bytes; boxes of 64 elements must fit the tensors
+    if (K < 64 || K % 8 != 0 || M < 128 || M % 8 != 0) return 0;
+    if (T * B < 128 || T * B > INT32_MAX || K > INT32_MAX || M > INT32_MAX) return 0;
+    return 1;
+}
+
+int64_t snn_linear_lif_bwd_workspace_bytes(int64_t T, int64_t B, int64_t K, int64_t M, int dtype) {
+    if (!snn_linear_lif_bwd_supported(T, B, K, M, dtype)) return -static_cast<int64_t>(SNN_ERR_UNSUPPORTED);
+    return static_cast<int64_t>(workspace_layout(T, B, M).total);
+}
+
+int snn_linear_lif_bwd(const void* x, const void* weight, const void* current, const void* grad_spike,
+                       void* grad_x, void* grad_weight, float* grad_bias, int64_t T, int64_t B, int64_t K,
+                       int64_t M, int dtype, int grad_weight_dtype, float alpha, float thresh, float beta,
+                       float interval, void* workspace, size_t workspace_bytes, void* stream) {
+    if (dtype != SNN_BF16 && dtype != SNN_F32 && dtype != SNN_F16 && dtype != SNN_F64) return SNN_ERR_DTYPE;
+    if (grad_weight_dtype != SNN_BF16 && grad_weight_dtype != SNN_F32) return SNN_ERR_DTYPE;
+    if (T < 1 || B < 1 || K < 1 || M < 1) return SNN_ERR_SHAPE;
+    if (!snn_linear_lif_bwd_supported(T, B, K, M, dtype)) return SNN_ERR_UNSUPPORTED;
+    if (!current || !grad_spike) return SNN_ERR_NULL;
+    if ((grad_x && !weight) || (grad_weight && !x)) return SNN_ERR_NULL;
+    auto al = [](const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; };
+    if (!al(x, 16) || !al(weight, 16) || !al(current, 16) || !al(grad_spike, 16) || !al(grad_x, 16) ||
+        !al(grad_weight, 16) || !al(grad_bias, 4))
+        return SNN_ERR_ALIGN;
+    const Workspace ws = workspace_layout(T, B, M);
+    if (!workspace || workspace_bytes < ws.total || !al(workspace, 256)) return SNN_ERR_WORKSPACE;
+    if (grad_bias != nullptr && grad_weight == nullptr) return SNN_ERR_NULL;   // the bias sum rides on the weight GEMM
+
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const int Ti = static_cast<int>(T), Bi = static_cast<int>(B), Mi = static_cast<int>(M);
+    void* du = workspace;
+    float* partials = grad_bias != nullptr
+        ? reinterpret_cast<float*>(static_cast<unsigned char*>(workspace) + ws.du_bytes) : nullptr;
+    switch (du_tmax(T)) {
+        case 2: launch_du<2>(current, grad_spike, du, partials, Ti, Bi, Mi, alpha, thresh, beta, interval, st); break;
+        case 4: launch_du<4>(current, grad_spike, du, partials, Ti, Bi, Mi, alpha, thresh, beta, interval, st); break;
+        case 8: launch_du<8>(current, grad_spike, du, partials, Ti, Bi, Mi, alpha, thresh, beta, interval, st); break;
+        default: launch_du<16>(current, grad_spike, du, partials, Ti, Bi, Mi, alpha, thresh, beta, interval, st); break;
+    }
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) { snn_internal::set_last_cuda_error(static_cast<int>(e)); return SNN_ERR_CUDA; }
+
+    const int64_t TB = T * B;
+    GemmParams P;
+    P.count = 0;
+    P.total_tiles = 0;
+    bool maps_ok = true;
+    auto add = [&](GemmProblem& pr, int64_t I, int64_t J, int64_t R) {
+        pr.tiles_i = static_cast<int>((I + TI - 1) / TI);
+        pr.tiles_j = static_cast<int>((J + TJ - 1) / TJ);
+        pr.num_rb = static_cast<int>((R + BR - 1) / BR);
+        pr.rows = static_cast<int>(I);
+        pr.tile_begin = P.total_tiles;
+        P.total_tiles += pr.tiles_i * pr.tiles_j;
+        ++P.count;
+    };
+    if (grad_x != nullptr) {
+        // grad_x[(t,b), k] = sum_m dU[(t,b), m] W[m, k]
+        GemmProblem& pr = P.p[P.count];
+        pr.a_mn = 0;
+        pr.out_f32 = 0;
+        pr.bias_partials = nullptr; pr.grad_bias = nullptr; pr.partial_rows = 0;
+        maps_ok = maps_ok && map2d(&pr.map_a, du, M, TB, 64, TI);            // {64 m, 128 (t,b)}
+        maps_ok = maps_ok && map2d(&pr.map_b, weight, K, M, 64, 64);         // {64 k, 64 m}
+        maps_ok = maps_ok && map2d(&pr.map_d, grad_x, K, TB, 64, TI);        // {64 k = 128 bytes, 128 (t,b)}
+        add(pr, TB, K, M);
+    }
+    if (grad_weight != nullptr) {
+        // grad_W[m, k] = sum_(t,b) dU[(t,b), m] x[(t,b), k]
+        GemmProblem& pr = P.p[P.count];
+        const bool f32 = grad_weight_dtype == SNN_F32;
+        pr.a_mn = 1;
+        pr.out_f32 = f32 ? 1 : 0;
+        pr.bias_partials = partials; pr.grad_bias = grad_bias; pr.partial_rows = ws.partial_rows;
+        maps_ok = maps_ok && map2d(&pr.map_a, du, M, TB, 64, 64);            // {64 m, 64 (t,b)}
+        maps_ok = maps_ok && map2d(&pr.map_b, x, K, TB, 64, 64);             // {64 k, 64 (t,b)}
+        maps_ok = maps_ok && map2d(&pr.map_d, grad_weight, K, M, f32 ? 32 : 64, TI, f32);
+        add(pr, M, K, TB);
+    }
+    if (!maps_ok) {
+        snn_internal::set_last_cuda_error(static_cast<int>(cudaErrorInvalidValue));
+        return SNN_ERR_CUDA;
+    }
+    if (P.count == 0) return SNN_OK;
+
+    static_assert(sizeof(GemmStorage) + 1024 <= 227 * 1024, "shared memory budget");
+    const size_t smem = sizeof(GemmStorage) + 1024;
+    e = cudaFuncSetAttribute(bwd_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    const int sms = sm_count();
+    if (e == cudaSuccess && sms <= 0) e = cudaErrorInvalidDevice;
+    if (e != cudaSuccess) { snn_internal::set_last_cuda_error(static_cast<int>(e)); return SNN_ERR_CUDA; }
+    const int grid = P.total_tiles < sms ? P.total_tiles : sms;
+    bwd_gemm_kernel<<<grid, kThreadsG, smem, st>>>(P);
+    e = cudaGetLastError();
+    if (e != cudaSuccess) { snn_internal::set_last_cuda_error(static_cast<int>(e)); return SNN_ERR_CUDA; }
+    return SNN_OK;
+}
+
+}  // extern "C"

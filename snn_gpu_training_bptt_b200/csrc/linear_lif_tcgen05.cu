@@ -31,23 +31,21 @@
 // a second epilogue group, warps 6-9. Shared-memory stages of {W tile, X tile} in bf16 with the
 // 128-byte swizzle; full/empty mbarriers per stage; tcgen05.commit frees a stage when the MMAs
 // that read it retire and finally signals the accumulator. Every mbarrier wait is bounded (~1 s):
-// on expiry the thread records an error code in g_linear_lif_error, everybody falls through to
+// on expiry the thread records an error code in g_tc_error, everybody falls through to
 // the common exit, and TMEM is released. No multicast loads anywhere: every CTA fetches its own
 // operands.
 #include "../../include/snn_b200.h"
 
-#include <cuda.h>
-#include <cuda_bf16.h>
-#include <cuda_runtime.h>
-#include <stdint.h>
-#include <stdlib.h>
-#include <type_traits>
+#include "tcgen05_common.cuh"
 
 namespace snn_internal {
-void set_last_cuda_error(int e);   // defined in lif_capi.cu
+void set_last_cuda_error(int e);      // defined in lif_capi.cu
+int linear_lif_bwd_error(int reset);   // error word of the backward kernels, linear_lif_bwd_tcgen05.cu
 }
 
 namespace {
+
+using namespace snn_tc;
 
 constexpr int BM = 128;            // output neurons per CTA (= TMEM lanes)
 constexpr int BN = 128;            // (t, b) pairs per CTA (= TMEM columns)
@@ -58,9 +56,6 @@ constexpr int kThreads = 192;
 constexpr uint32_t kStageBytesA = BM * BK * 2;
 constexpr uint32_t kStageBytesB = BN * BK * 2;
 constexpr uint32_t kTmemCols = 128;
-constexpr long long kWaitCycles = 2000000000LL;       // ~1 s
-
-__device__ int g_linear_lif_error = 0;
 
 struct __align__(1024) SharedStorage {
     __nv_bfloat16 a[STAGES][BM * BK];
@@ -70,96 +65,6 @@ struct __align__(1024) SharedStorage {
     uint64_t accum_full;
     uint32_t tmem_base;
 };
-
-__device__ __forceinline__ uint32_t smem_u32(const void* p) {
-    return static_cast<uint32_t>(__cvta_generic_to_shared(p));
-}
-__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
-                 : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok)
-        : "r"(smem_u32(bar)), "r"(parity)
-        : "memory");
-    return ok != 0;
-}
-// Only the FIRST failure is kept (a producer that gives up makes the MMA issuer and the epilogue
-// give up later: their codes would hide the cause).
-__device__ __forceinline__ void record_error(int code) { atomicCAS(&g_linear_lif_error, 0, code); }
-// false if the barrier did not reach the phase within the limit, or if another role (of any CTA)
-// has already recorded a failure: dependent waits then return at once instead of running out
-// their own limit one after the other.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
-    if (mbar_try_wait(bar, parity)) return true;
-    const long long t0 = clock64();
-    for (uint32_t spins = 1;; ++spins) {
-        if (mbar_try_wait(bar, parity)) return true;
-        if (clock64() - t0 > kWaitCycles) return false;
-        if ((spins & 63u) == 0u && *reinterpret_cast<volatile int*>(&g_linear_lif_error) != 0) return false;
-    }
-}
-
-__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-        ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1)
-        : "memory");
-}
-__device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1,
-                                            int c2) {
-    asm volatile(
-        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
-        ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2)
-        : "memory");
-}
-
-// Shared-memory matrix descriptor for a K-major tile whose rows are 128 bytes (64 bf16) with the
-// 128-byte swizzle: start address >> 4 in bits [0,14), leading byte offset (unused for swizzled
-// K-major, encoded 1) in [16,30), stride byte offset = 1024 B between 8-row groups in [32,46),
-// descriptor version 1 in [46,48), layout type 2 (SWIZZLE_128B) in [61,64).
-__device__ __forceinline__ uint64_t umma_desc_sw128(const void* tile) {
-    uint64_t d = static_cast<uint64_t>((smem_u32(tile) >> 4) & 0x3FFF);
-    d |= static_cast<uint64_t>(1) << 16;
-    d |= static_cast<uint64_t>(1024 >> 4) << 32;
-    d |= static_cast<uint64_t>(1) << 46;
-    d |= static_cast<uint64_t>(2) << 61;
-    return d;
-}
-// Instruction descriptor, kind::f16: D fp32 (bits [4,6) = 1), A and B bf16 ([7,10) = [10,13) = 1),
-// both K-major (bits 15, 16 = 0), N >> 3 in [17,23), M >> 4 in [24,29).
-__host__ __device__ constexpr uint32_t umma_idesc_bf16(int m, int n) {
-    return (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(n >> 3) << 17) |
-           (static_cast<uint32_t>(m >> 4) << 24);
-}
-__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
-                                          uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}"
-        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(0u)
-        : "memory");
-}
-__device__ __forceinline__ void umma_commit(uint64_t* bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
-                 : "memory");
-}
-__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-        : "r"(taddr));
-}
 
 // T time steps, 128/T batch items per CTA tile.
 template <int T>
@@ -313,53 +218,6 @@ struct __align__(1024) PersistentStorage {
     uint32_t tmem_base;
     uint32_t epi_ok[2];
 };
-
-__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-__device__ __forceinline__ void tma_store_3d(const CUtensorMap* map, const void* src, int c0, int c1, int c2) {
-    asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];" ::"l"(map),
-                 "r"(smem_u32(src)), "r"(c0), "r"(c1), "r"(c2)
-                 : "memory");
-}
-__device__ __forceinline__ void group_barrier(int g) {      // the 128 threads of epilogue group g
-    asm volatile("bar.sync %0, 128;" ::"r"(1 + g) : "memory");
-}
-
-// tcgen05.ld of NCOL (2, 4, 8 or 16) consecutive columns of this warp's 32 lanes into r[0..NCOL)
-template <int NCOL>
-__device__ __forceinline__ void tmem_ld_cols(uint32_t taddr, uint32_t* r) {
-    if constexpr (NCOL == 16) {
-        asm volatile(
-            "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
-            : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-              "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-            : "r"(taddr));
-    } else if constexpr (NCOL == 8) {
-        asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
-                     : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
-                     : "r"(taddr));
-    } else if constexpr (NCOL == 4) {
-        asm volatile("tcgen05.ld.sync.aligned.32x32b.x4.b32 {%0, %1, %2, %3}, [%4];"
-                     : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
-                     : "r"(taddr));
-    } else {
-        static_assert(NCOL == 2, "2, 4, 8 or 16 columns");
-        asm volatile("tcgen05.ld.sync.aligned.32x32b.x2.b32 {%0, %1}, [%2];" : "=r"(r[0]), "=r"(r[1]) : "r"(taddr));
-    }
-}
-// Waits for the loads issued so far. The 32 registers of a unit are passed through the statement
-// so that no use of them can be scheduled ahead of the wait.
-__device__ __forceinline__ void tmem_ld_wait32(uint32_t (&r)[32]) {
-    asm volatile("tcgen05.wait::ld.sync.aligned;"
-                 : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]),
-                   "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]),
-                   "+r"(r[15]), "+r"(r[16]), "+r"(r[17]), "+r"(r[18]), "+r"(r[19]), "+r"(r[20]), "+r"(r[21]),
-                   "+r"(r[22]), "+r"(r[23]), "+r"(r[24]), "+r"(r[25]), "+r"(r[26]), "+r"(r[27]), "+r"(r[28]),
-                   "+r"(r[29]), "+r"(r[30]), "+r"(r[31])
-                 :
-                 : "memory");
-}
 
 // LIF epilogue of one accumulator tile for epilogue group g (thread = TMEM lane = output neuron
 // `row` of the tile). The group walks its 32-column units (32/T batch items x all T steps = 32
@@ -795,62 +653,6 @@ linear_lif_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
     }
 }
 
-// ---- host side ---------------------------------------------------------------------------------
-using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn encode_tiled() {
-    static EncodeTiledFn fn = nullptr;
-    if (fn == nullptr) {
-        void* p = nullptr;
-        cudaDriverEntryPointQueryResult q;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
-            q == cudaDriverEntryPointSuccess)
-            fn = reinterpret_cast<EncodeTiledFn>(p);
-    }
-    return fn;
-}
-
-// swizzled = operand tiles read by the MMA (128-byte swizzle); plain = output tiles written by TMA stores
-bool make_map(CUtensorMap* map, const void* base, int rank, const cuuint64_t* dims, const cuuint64_t* strides,
-              const cuuint32_t* box, bool swizzled) {
-    EncodeTiledFn enc = encode_tiled();
-    if (enc == nullptr) return false;
-    const cuuint32_t elem_strides[3] = {1, 1, 1};
-    return enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, static_cast<cuuint32_t>(rank), const_cast<void*>(base), dims,
-               strides, box, elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE,
-               swizzled ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
-               CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
-}
-
-// Encoding a tensor map costs a few microseconds of host time, comparable to the kernel itself for
-// small layers, and a training loop calls with the same buffers step after step: keep the last
-// few maps keyed by everything that went into them.
-struct MapKey {
-    const void* base; int rank; cuuint64_t dims[3]; cuuint32_t box[3]; bool swizzled;
-    bool operator==(const MapKey& o) const {
-        if (base != o.base || rank != o.rank || swizzled != o.swizzled) return false;
-        for (int i = 0; i < 3; ++i) if (dims[i] != o.dims[i] || box[i] != o.box[i]) return false;
-        return true;
-    }
-};
-bool cached_map(CUtensorMap* out, const void* base, int rank, const cuuint64_t* dims, const cuuint64_t* strides,
-                const cuuint32_t* box, bool swizzled = true) {
-    constexpr int kSlots = 16;
-    thread_local MapKey keys[kSlots];
-    thread_local CUtensorMap maps[kSlots];
-    thread_local int used = 0, next = 0;
-    MapKey k{base, rank, {dims[0], dims[1], rank > 2 ? dims[2] : 1}, {box[0], box[1], rank > 2 ? box[2] : 1}, swizzled};
-    for (int i = 0; i < used; ++i)
-        if (keys[i] == k) { *out = maps[i]; return true; }
-    if (!make_map(out, base, rank, dims, strides, box, swizzled)) return false;
-    const int slot = used < kSlots ? used++ : (next++ % kSlots);
-    keys[slot] = k;
-    maps[slot] = *out;
-    return true;
-}
-
 template <int T>
 int launch(const CUtensorMap& mw, const CUtensorMap& mx, const float* bias, void* current, void* spike, int B, int K,
            int M, float alpha, float thresh, cudaStream_t st) {
@@ -864,17 +666,6 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mx, const float* bias, void
     e = cudaGetLastError();
     if (e != cudaSuccess) { snn_internal::set_last_cuda_error(static_cast<int>(e)); return SNN_ERR_CUDA; }
     return SNN_OK;
-}
-
-int sm_count() {
-    thread_local int dev_cached = -1, sms = 0;
-    int dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess) return 0;
-    if (dev != dev_cached) {
-        if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return 0;
-        dev_cached = dev;
-    }
-    return sms;
 }
 
 template <int T, int WN>
@@ -1041,14 +832,16 @@ int snn_linear_lif_fwd(const void* x, const void* weight, const float* bias, voi
 }
 
 int snn_linear_lif_error(int reset) {
+    // the forward and the backward kernels keep an error word each; report the forward's first
+    const int bwd = snn_internal::linear_lif_bwd_error(reset);
     int v = 0;
-    cudaError_t e = cudaMemcpyFromSymbol(&v, g_linear_lif_error, sizeof(int));
+    cudaError_t e = cudaMemcpyFromSymbol(&v, g_tc_error, sizeof(int));
     if (e != cudaSuccess) { snn_internal::set_last_cuda_error(static_cast<int>(e)); return -1; }
     if (reset && v != 0) {
         const int zero = 0;
-        cudaMemcpyToSymbol(g_linear_lif_error, &zero, sizeof(int));
+        cudaMemcpyToSymbol(g_tc_error, &zero, sizeof(int));
     }
-    return v;
+    return v != 0 ? v : bwd;
 }
 
 }  // extern "C"

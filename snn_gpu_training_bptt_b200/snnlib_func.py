@@ -171,26 +171,45 @@ fc_func = FcFunc.apply
 
 class FcFireFunc(torch.autograd.Function):
     """Synaptic linear followed by LIF: ``fire_func(fc_func(x, W, b))`` as one op (an addition to
-    the reference's set of Functions). For bf16 problems the tcgen05 kernel covers, forward is a
-    single fused GEMM + LIF-epilogue launch; otherwise one library GEMM and the LIF kernel. The
-    LIF input current is saved (bf16 / input dtype) for the backward pass: LIF reverse pass, then
-    the two gradient GEMMs."""
+    the reference's set of Functions). For bf16 problems the tcgen05 kernels cover, forward is a
+    single fused GEMM + LIF-epilogue launch and backward is the library's own pair of launches
+    (LIF reverse pass, then both gradient GEMMs in one persistent tcgen05 kernel); otherwise one
+    library GEMM and the LIF kernels each way. The LIF input current is saved (bf16 / input dtype)
+    for the backward pass, and so is the bf16 copy of an fp32 master weight, so the weight is cast
+    once per step."""
 
     @staticmethod
     def forward(ctx, spatial, weight_fc, bias_fc):
-        if spatial.dim() == 3 and _capi.linear_lif_supported(spatial, weight_fc):
-            current, spike = _capi.linear_lif_fwd(spatial, weight_fc, bias_fc, alpha, thresh)
+        fused = spatial.dim() == 3 and _capi.linear_lif_supported(spatial, weight_fc)
+        if fused:
+            weight_op = weight_fc if weight_fc.dtype == torch.bfloat16 else weight_fc.to(torch.bfloat16)
+            current, spike = _capi.linear_lif_fwd(spatial, weight_op, bias_fc, alpha, thresh)
         else:
+            weight_op = weight_fc
             current = snnlib.fc_fp(spatial, weight_fc, bias_fc)
             spike = snnlib.fire_s_fp(current, alpha, thresh)
-        ctx.save_for_backward(spatial, weight_fc, bias_fc, current)
+        ctx.save_for_backward(spatial, weight_op, bias_fc, current)
+        ctx.fused = fused and _capi.linear_lif_bwd_supported(spatial, weight_op)
+        ctx.weight_dtype = weight_fc.dtype
         return spike
 
     @staticmethod
     def backward(ctx, grad_spike):
-        spatial, weight_fc, bias_fc, current = ctx.saved_tensors
+        spatial, weight_op, bias_fc, current = ctx.saved_tensors
+        if ctx.fused:
+            need_x, need_w, need_b = ctx.needs_input_grad[0], ctx.needs_input_grad[1], \
+                bias_fc is not None and ctx.needs_input_grad[2]
+            out_dtype = ctx.weight_dtype if ctx.weight_dtype in (torch.float32, torch.bfloat16) else torch.float32
+            gx, gw, gb = _capi.linear_lif_bwd(spatial, weight_op, current, grad_spike, alpha, thresh, beta,
+                                              interval, need_x, need_w, need_b, out_dtype)
+            if gw is not None and gw.dtype != ctx.weight_dtype:
+                gw = gw.to(ctx.weight_dtype)
+            if gb is not None and gb.dtype != bias_fc.dtype:
+                gb = gb.to(bias_fc.dtype)
+            return gx, (gw if need_w else None), gb
         grad_current = snnlib.fire_bp(current, grad_spike, alpha, thresh, beta, interval)
-        return tuple(snnlib.fc_bp(spatial, grad_current, weight_fc, bias_fc, _DIM_FC))
+        gx, gw, gb = snnlib.fc_bp(spatial, grad_current, weight_op, bias_fc, _DIM_FC)
+        return gx, gw.to(ctx.weight_dtype), (gb if bias_fc is not None else None)
 
 
 fc_fire_func = FcFireFunc.apply
