@@ -145,54 +145,112 @@ def gbps(n_neurons, seconds):
     return (BYTES_FWD + BYTES_BWD) * T_STEPS * n_neurons / seconds / 1e9
 
 
+def cpu_reference_time(gold, n_sample, reps, threads):
+    import torch
+    torch.set_num_threads(threads)
+    gen = torch.Generator().manual_seed(1234)
+    x = 0.5 + torch.randn((T_STEPS, 1, n_sample), generator=gen)
+    g = torch.randn((T_STEPS, 1, n_sample), generator=gen)
+    best = float("inf")
+    for _ in range(reps):
+        t0 = time.perf_counter()
+        reference_fwd_bwd(gold, x, g)
+        best = min(best, time.perf_counter() - t0)
+    return best
+
+
 def cpu_baseline_block():
     cores = os.cpu_count() or 1
     n_sample = 1 << 22
-    t_torch = cpu_torch_port_time(n_sample, reps=3, threads=cores)
+    gold = reference_gold_op()
+    if gold is not None:
+        t_torch, kind = cpu_reference_time(gold, n_sample, reps=3, threads=cores), "reference"
+        what = "the reference's own gold_op.py (gold_fire + autograd, from oracle/_ref)"
+    else:
+        t_torch, kind = cpu_torch_port_time(n_sample, reps=3, threads=cores), "port"
+        what = "PyTorch-autograd port of the reference's gold_fire"
     t_c = cpu_c_port_time(1 << 24, reps=3)
     return {
-        "value": round(gbps(n_sample, t_torch), 3), "unit": "GB/s", "cores": cores, "kind": "port",
-        "sample": f"PyTorch-autograd port of the reference's gold_fire, fwd+bwd, T=8, N=2^22 "
+        "value": round(gbps(n_sample, t_torch), 3), "unit": "GB/s", "cores": cores, "kind": kind,
+        "sample": f"{what}, fwd+bwd, T=8, N=2^22 "
                   f"(1/16 of one GPU step), best of 3, {t_torch:.3f} s",
         "c_loops_value": round(gbps(1 << 24, t_c), 3),
         "c_loops_sample": f"plain-C OpenMP restatement, T=8, N=2^24, best of 3, {t_c:.3f} s",
     }
 
 
+def reference_gold_op():
+    """The reference's own CPU implementation of the path: its pure-PyTorch gold_op.py as installed,
+    unmodified, into oracle/_ref/ by oracle/build_oracle.install_reference(). None when absent."""
+    path = os.path.join(ROOT, "oracle", "_ref", "gold_op.py")
+    if not os.path.exists(path):
+        return None
+    import importlib.util
+    spec = importlib.util.spec_from_file_location("snn_reference_gold_op", path)
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod
+
+
+def reference_fwd_bwd(gold, x, g):
+    """One forward + backward of the reference's gold_fire (its globals set to this workload's
+    constants; gold_fire reads the step count from its module global)."""
+    gold.alpha, gold.beta, gold.interval, gold.thresh, gold.time_step = ALPHA, BETA, INTERVAL, THRESH, x.shape[0]
+    xr = x.detach().requires_grad_(True)
+    _, spikes = gold.gold_fire(xr)
+    spikes.backward(g)
+    return xr.grad
+
+
 def run_reference_arm(args):
-    """The reference's CPU implementation of the path (its pure-PyTorch gold op, restated in
-    oracle/lif_oracle.py because the reference checkout does not travel), all host threads."""
+    """The reference's CPU implementation of the path on all host threads: its own gold_op.py when
+    oracle/_ref/ holds it (kind "reference"), else the restatement in oracle/lif_oracle.py (kind
+    "port"). Each step is a bounded sample of the GPU arm's 2^26-neuron step; GB/s is normalised by
+    the sample's size."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
+    import torch
+    from oracle import lif_oracle as orc
     cores = os.cpu_count() or 1
-    probe = cpu_torch_port_time(1 << 18, reps=2, threads=cores)      # seconds per 2^18 neurons
-    budget = 90.0 / max(1, args.steps + args.warmup)                 # seconds per step
+    torch.set_num_threads(cores)
+    gold = reference_gold_op()
+    kind = "reference" if gold is not None else "port"
+    step_fn = (lambda x, g: reference_fwd_bwd(gold, x, g)) if gold is not None else (lambda x, g: orc.torch_fire_fwd_bwd(x, g))
+
+    def inputs(n):
+        gen = torch.Generator().manual_seed(1234)
+        return (0.5 + torch.randn((T_STEPS, 1, n), generator=gen), torch.randn((T_STEPS, 1, n), generator=gen))
+
+    x, g = inputs(1 << 18)
+    step_fn(x, g)
+    t0 = time.perf_counter()
+    step_fn(x, g)
+    probe = time.perf_counter() - t0                                   # seconds per 2^18 neurons
+    budget = 90.0 / max(1, args.steps + args.warmup)                   # seconds per step
     n_sample = 1 << 18
     while n_sample < (1 << 23) and probe * (2 * n_sample / (1 << 18)) <= budget:
         n_sample *= 2
-    import torch
-    from oracle import lif_oracle as orc
-    torch.set_num_threads(cores)
-    gen = torch.Generator().manual_seed(1234)
-    x = 0.5 + torch.randn((T_STEPS, 1, n_sample), generator=gen)
-    g = torch.randn((T_STEPS, 1, n_sample), generator=gen)
+    x, g = inputs(n_sample)
     for _ in range(args.warmup):
-        orc.torch_fire_fwd_bwd(x, g)
+        step_fn(x, g)
     t0 = time.perf_counter()
     for _ in range(args.steps):
-        orc.torch_fire_fwd_bwd(x, g)
+        step_fn(x, g)
     dt = (time.perf_counter() - t0) / args.steps
     value = round(gbps(n_sample, dt), 3)
-    sample = (f"PyTorch-autograd port of the reference's gold_fire on host cores, fwd+bwd, T=8, "
-              f"N={n_sample} neurons per step (bounded sample of the 2^26-neuron step)")
+    what = ("the reference's own snnlib/example/gold_op.py (gold_fire + autograd)" if gold is not None
+            else "PyTorch-autograd port of the reference's gold_fire (oracle/_ref not installed)")
+    sample = f"{what} on {cores} host threads, fwd+bwd, fp32, T=8, N=2^{n_sample.bit_length() - 1} neurons per step"
     print(json.dumps({
         "impl": "reference", "metric": "lif_fwd_bwd_hbm_gbps", "value": value, "unit": "GB/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": round(dt * 1e3, 3), "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": WORKLOAD, "sample_neurons_per_step": n_sample},
-        "cpu_baseline": {"value": value, "unit": "GB/s", "cores": cores, "kind": "port", "sample": sample},
+        "config": {"workload": WORKLOAD.replace("N=2^26 per GPU", f"N=2^{n_sample.bit_length() - 1} per step (a bounded sample "
+                                                "of the GPU arm's 2^26-neuron step; GB/s is size-normalised)"),
+                   "T": T_STEPS, "neurons_per_step": n_sample},
+        "cpu_baseline": {"value": value, "unit": "GB/s", "cores": cores, "kind": kind, "sample": sample},
         "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }))
@@ -245,27 +303,35 @@ def run_ours(args):
         step()
     barrier()
 
+    # The K timed steps take ~0.3 s at most; the K-step block (barrier + synchronize on both sides,
+    # CUDA events on the launching stream) is repeated until at least MIN_TIMED_MS of device time has
+    # been measured, so that the clock sampler sees the GPU under load, and the MEDIAN block is the
+    # one reported. Every rank runs the same number of blocks (the decision uses the max over ranks).
+    MIN_TIMED_MS, MAX_BLOCKS = 1000.0, 200
     ev = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(args.steps)]
     e_start, e_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    blocks, timed_ms = [], 0.0
     with ClockSampler(local) as clocks:
-        barrier()
-        e_start.record(stream)
-        for k in range(args.steps):
-            ev[k][0].record(stream)
-            _capi.check("snn_lif_fwd", L.snn_lif_fwd(px, ps, None, None, T, N, 0, ALPHA, THRESH, sp))
-            ev[k][1].record(stream)
-            _capi.check("snn_lif_bwd", L.snn_lif_bwd(px, pg, pgx, T, N, 0, ALPHA, THRESH, BETA, INTERVAL, None, 0, sp))
-            ev[k][2].record(stream)
-        e_end.record(stream)
-        barrier()
-    total_ms = e_start.elapsed_time(e_end)
-    fwd_ms = statistics.mean(e[0].elapsed_time(e[1]) for e in ev)
-    bwd_ms = statistics.mean(e[1].elapsed_time(e[2]) for e in ev)
-
-    if world > 1:
-        t = torch.tensor([total_ms, fwd_ms, bwd_ms], device=dev, dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        total_ms, fwd_ms, bwd_ms = (float(v) for v in t.tolist())
+        while timed_ms < MIN_TIMED_MS and len(blocks) < MAX_BLOCKS:
+            barrier()
+            e_start.record(stream)
+            for k in range(args.steps):
+                ev[k][0].record(stream)
+                _capi.check("snn_lif_fwd", L.snn_lif_fwd(px, ps, None, None, T, N, 0, ALPHA, THRESH, sp))
+                ev[k][1].record(stream)
+                _capi.check("snn_lif_bwd", L.snn_lif_bwd(px, pg, pgx, T, N, 0, ALPHA, THRESH, BETA, INTERVAL, None, 0, sp))
+                ev[k][2].record(stream)
+            e_end.record(stream)
+            barrier()
+            blk = [e_start.elapsed_time(e_end), statistics.mean(e[0].elapsed_time(e[1]) for e in ev),
+                   statistics.mean(e[1].elapsed_time(e[2]) for e in ev)]
+            if world > 1:
+                t = torch.tensor(blk, device=dev, dtype=torch.float64)
+                dist.all_reduce(t, op=dist.ReduceOp.MAX)
+                blk = [float(v) for v in t.tolist()]
+            blocks.append(blk)
+            timed_ms += blk[0]
+    total_ms, fwd_ms, bwd_ms = sorted(blocks, key=lambda b: b[0])[len(blocks) // 2]
     ms_per_step = total_ms / args.steps
     value = gbps(N * world, ms_per_step / 1e3)
 
@@ -309,22 +375,53 @@ def run_ours(args):
         del hx, hg, hs, hgx, pipe
         break
 
-    # ---- second half of the metric: spiking-CNN training samples/sec (data-parallel) ----------
-    trainer = None
-    if not args.no_trainer:
+    # ---- fused synaptic linear + LIF layer (tensor-core leg), rank 0's GPU -----------------------
+    linear_lif = None
+    if not args.no_linear_lif:
         del x, g, spike, gx
         torch.cuda.empty_cache()
+        if rank == 0:
+            with ClockSampler(local) as lin_clocks:
+                linear_lif = linear_lif_block(dev, 256, reps=40)
+            linear_lif["clocks"] = lin_clocks.summary()
+        barrier()
+
+    # ---- second half of the metric: spiking-CNN training samples/sec (data-parallel) ----------
+    trainer, trainer_resnet = None, None
+    if not args.no_trainer:
+        if args.no_linear_lif:
+            del x, g, spike, gx
+        torch.cuda.empty_cache()
         from snn_gpu_training_bptt_b200.example import train_synthetic
-        tr = train_synthetic.run("vgg", time_steps=8, batch=64, steps=args.trainer_steps, warmup=5,
-                                 precision="bf16")
-        trainer = {"metric": "spiking_cnn_train_samples_per_s", "value": round(tr["samples_per_s"], 1),
+
+        def trainer_leg(name, time_steps, batch, steps, workload):
+            tr = train_synthetic.run(name, time_steps=time_steps, batch=batch, steps=steps, warmup=5, precision="bf16")
+            leg = {"metric": "spiking_cnn_train_samples_per_s", "value": round(tr["samples_per_s"], 1),
                    "unit": "samples/s", "ms_per_step": round(tr["ms_per_step"], 3),
-                   "config": {"workload": "VGG-style spiking CNN (conv 128-128-P-256-256-P-512-512-P, fc 8192-1024-10, "
-                                          "LIF after every conv/fc), T=8, batch 64 per GPU, synthetic 3x32x32 U(0,1) "
-                                          "images, SGD momentum 0.9, bf16 synaptic ops + fp32 LIF state",
+                   "config": {"workload": workload,
                               "parallelism": f"dp{world}, bucketed NCCL all-reduce overlapped with backward"},
                    "steps": tr["steps"], "params": tr["params"], "final_loss": round(tr["final_loss"], 4),
-                   "h2d_bytes_per_step": tr["h2d_bytes_per_step"], "d2h_bytes_per_step": tr["d2h_bytes_per_step"]}
+                   "h2d_bytes_per_step": tr["h2d_bytes_per_step"], "d2h_bytes_per_step": tr["d2h_bytes_per_step"],
+                   "grad_bucket_bytes": tr["bucket_bytes"]}
+            if world > 1:
+                # the same captured step with the all-reduces left out: the difference is the
+                # communication time that backward does not hide
+                quiet = train_synthetic.run(name, time_steps=time_steps, batch=batch, steps=steps, warmup=5,
+                                            precision="bf16", communicate=False)
+                leg["ms_per_step_without_allreduce"] = round(quiet["ms_per_step"], 3)
+                leg["exposed_comm_ms"] = round(tr["ms_per_step"] - quiet["ms_per_step"], 3)
+            return leg
+
+        trainer = trainer_leg("vgg", 8, 64, args.trainer_steps,
+                              "VGG-style spiking CNN (conv 128-128-P-256-256-P-512-512-P, fc 8192-1024-10, "
+                              "LIF after every conv/fc), T=8, batch 64 per GPU, synthetic 3x32x32 U(0,1) "
+                              "images, SGD momentum 0.9, bf16 synaptic ops + fp32 LIF state")
+        if not args.no_resnet:
+            trainer_resnet = trainer_leg("resnet19", 16, 128, max(5, args.trainer_steps // 3),
+                                         "ResNet-19-style spiking network (3x3 stem, 3/3/2 residual blocks of "
+                                         "128/256/512 channels, LIF after every conv and after each add), T=16, "
+                                         "batch 128 per GPU, synthetic 3x32x32 U(0,1) images, SGD momentum 0.9, "
+                                         "bf16 synaptic ops + fp32 LIF state")
 
     if rank == 0:
         peak, peak_src = measured_peak()
@@ -350,10 +447,22 @@ def run_ours(args):
                          "frac": round(bwd_gbs / peak, 4), "traffic": traffic,
                          "algorithmic_bytes_per_launch": BYTES_BWD * T * N, "peak_source": peak_src},
             "clocks": clocks.summary(),
+            "timed_blocks": len(blocks), "timed_region_ms": round(timed_ms, 1),
             "e2e": e2e,
             "gpu_launches": 2 * args.steps,
             "trainer": trainer,
+            "trainer_resnet19": trainer_resnet,
+            "linear_lif": linear_lif,
         }
+        # flat copies of the nested legs (parsers that keep only top-level scalars still see them)
+        if linear_lif is not None:
+            for k in ("fwd_us", "bwd_us", "fwd_bwd_us", "fwd_tflops", "fwd_bwd_tflops", "fwd_frac", "fwd_bwd_frac"):
+                out["linear_lif_" + k] = linear_lif[k]
+        for prefix, leg in (("trainer", trainer), ("trainer_resnet19", trainer_resnet)):
+            if leg is not None:
+                out[prefix + "_samples_per_s"] = leg["value"]
+                out[prefix + "_ms_per_step"] = leg["ms_per_step"]
+                out[prefix + "_exposed_comm_ms"] = leg.get("exposed_comm_ms")
         if world == 1 and not args.no_cpu:
             out["cpu_baseline"] = cpu_baseline_block()
             if trainer is not None:
@@ -534,55 +643,104 @@ def run_bn_lif(args):
         "reference_traffic_bytes_per_neuron_step": "8 fwd + 8 (u rebuild) + 12 (sums) + 16 (input grad) = 44"}))
 
 
+def bf16_peak_tflops():
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            return float(json.load(f)["bf16_tflops"]), "measured (MEASURED_PEAKS.json bf16_tflops, cuBLAS burst)"
+    except Exception:
+        return 1590.0, "fallback (no MEASURED_PEAKS.json)"
+
+
+def linear_lif_block(dev, batch=256, reps=20, with_library=False):
+    """Fused synaptic linear + LIF layer (T=8, batch 256, 2048 -> 2048; Bernoulli(0.2) input spikes,
+    Kaiming-uniform weights, bf16 operands): device time of the forward kernel, of the backward pair
+    (dU kernel + the persistent kernel with both gradient GEMMs) and of both, through the C ABI,
+    by CUDA-graph replay (a launch of ~15 us cannot be timed eagerly from Python)."""
+    import torch
+    from snn_gpu_training_bptt_b200 import _capi
+    T, B, K, M = 8, batch, 2048, 2048
+    L, sp, P = _capi.lib(), _capi._stream(dev), _capi._ptr
+    torch.manual_seed(1234)
+    lin = torch.nn.Linear(K, M).to(dev)
+    x = (torch.rand((T, B, K), device=dev) < 0.2).to(torch.bfloat16)
+    w = lin.weight.detach().to(torch.bfloat16)
+    bias = lin.bias.detach().float()
+    gs = torch.randn((T, B, M), device=dev).to(torch.bfloat16)
+    cur, spk = torch.empty((T, B, M), dtype=torch.bfloat16, device=dev), torch.empty((T, B, M), dtype=torch.bfloat16, device=dev)
+    gx, gw, gb = torch.empty_like(x), torch.empty((M, K), device=dev), torch.empty(M, device=dev)
+    need = L.snn_linear_lif_bwd_workspace_bytes(T, B, K, M, 1)
+    ws = torch.empty(need, dtype=torch.uint8, device=dev)
+
+    def fwd():
+        # torch.cuda.graph captures on a side stream: look the current stream up at call time
+        rc = L.snn_linear_lif_fwd(P(x), P(w), P(bias), P(cur), P(spk), T, B, K, M, 1, ALPHA, THRESH, _capi._stream(dev))
+        assert rc == 0, rc
+
+    def bwd(want_gemms=True):
+        rc = L.snn_linear_lif_bwd(P(x), P(w), P(cur), P(gs), P(gx) if want_gemms else None, P(gw) if want_gemms else None,
+                                  P(gb) if want_gemms else None, T, B, K, M, 1, 0, ALPHA, THRESH, BETA, INTERVAL,
+                                  P(ws), need, _capi._stream(dev))
+        assert rc == 0, rc
+
+    fwd()
+    torch.cuda.synchronize(dev)
+    t_f = _time_graphed(fwd, reps)
+    t_b = _time_graphed(bwd, reps)
+    t_du = _time_graphed(lambda: bwd(False), reps)
+    t_fb = _time_graphed(lambda: (fwd(), bwd()), reps)
+    assert _capi.linear_lif_error() == 0
+    peak, peak_src = bf16_peak_tflops()
+    flops = 2.0 * T * B * K * M
+    tf = lambda n, ms: n * flops / ms / 1e9
+    out = {"workload": f"fc 2048->2048 + LIF, T=8, batch {B}, bf16 operands, fp32 accumulation and LIF state",
+           "fwd_us": round(t_f * 1e3, 2), "bwd_us": round(t_b * 1e3, 2), "fwd_bwd_us": round(t_fb * 1e3, 2),
+           "bwd_du_kernel_us": round(t_du * 1e3, 2),
+           "fwd_tflops": round(tf(1, t_f), 1), "bwd_tflops": round(tf(2, t_b), 1), "fwd_bwd_tflops": round(tf(3, t_fb), 1),
+           "fwd_frac": round(tf(1, t_f) / peak, 4), "bwd_frac": round(tf(2, t_b) / peak, 4),
+           "fwd_bwd_frac": round(tf(3, t_fb) / peak, 4), "peak_tflops": peak, "peak_source": peak_src,
+           "kernels": ["linear_lif_fwd_persistent_kernel<8,256>", "lif_du_kernel<8,8>", "bwd_gemm_kernel"],
+           "launches_per_step": 3, "how": "CUDA-graph replay of 10 calls, median of %d replays" % reps}
+    if with_library:
+        xr, wr = x.view(T * B, K), w
+        t_lib = _time_graphed(lambda: torch.nn.functional.linear(xr, wr), reps)
+        out["cublas_gemm_alone_us"] = round(t_lib * 1e3, 2)
+    return out
+
+
 def run_linear_lif(args):
-    """Synaptic linear followed by LIF (T=8, batch 256, 2048 -> 2048): Bernoulli(0.2) input spikes,
-    Kaiming-uniform weights. Forward alone (fused tcgen05 kernel vs library GEMM + LIF kernel) and
-    forward + BPTT backward with weight, bias and input gradients."""
+    """Synaptic linear followed by LIF (T=8, batch 256, 2048 -> 2048): the library's own kernels
+    through the C ABI, then the same layer through the autograd ops (fused FcFire against the
+    unfused library-GEMM composition) in bf16 and fp32."""
     import torch
     from snn_gpu_training_bptt_b200 import _capi, snnlib, snnlib_func as sf
     dev = torch.device("cuda", 0)
     torch.cuda.set_device(dev)
-    T, B, K, M = 8, args.batch, 2048, 2048       # --batch 256 = the reference-sized layer
+    torch.backends.cuda.matmul.allow_tf32 = False
+    with ClockSampler(0) as clocks:
+        block = linear_lif_block(dev, args.batch, with_library=True)
+    block["clocks"] = clocks.summary()
+    print(json.dumps({"metric": "linear_lif_fwd_bwd_tflops", "value": block["fwd_bwd_tflops"], "unit": "TFLOP/s",
+                      "dtype": "bf16", "config": {"workload": block["workload"]}, "linear_lif": block}))
+    T, B, K, M = 8, args.batch, 2048, 2048
     torch.manual_seed(1234)
     lin = torch.nn.Linear(K, M).to(dev)
-    fwd_flops, all_flops = 2.0 * T * B * K * M, 2.0 * T * B * K * M * 3
-    torch.backends.cuda.matmul.allow_tf32 = False
-    peak_tf = None
-    try:
-        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
-            peak_tf = float(json.load(f)["bf16_tflops"])
-    except Exception:
-        peak_tf = 1590.0
-
-    def line(name, path, flops, ms, dtype):
-        tf = flops / ms / 1e9
-        print(json.dumps({"metric": name, "value": round(tf, 1), "unit": "TFLOP/s", "dtype": dtype,
-                          "ms": round(ms, 4), "frac_of_bf16_burst_peak": round(tf / peak_tf, 4),
-                          "config": {"workload": "fc 2048->2048 + LIF, T=8, batch %d" % B, "path": path}}))
-
-    xb = (torch.rand((T, B, K), device=dev) < 0.2).to(torch.bfloat16)
-    wb = lin.weight.detach().to(torch.bfloat16)
-    bias = lin.bias.detach().float()
-    assert _capi.linear_lif_supported(xb, wb)
-    ms = _time_graphed(lambda: _capi.linear_lif_fwd(xb, wb, bias, ALPHA, THRESH))
-    line("linear_lif_fwd_tflops", "fused: tcgen05 GEMM with the LIF recurrence in its epilogue (1 launch)", fwd_flops, ms, "bf16")
-    assert _capi.linear_lif_error() == 0
-    ms = _time_graphed(lambda: snnlib.fire_s_fp(snnlib.fc_fp(xb, wb, bias), ALPHA, THRESH))
-    line("linear_lif_fwd_tflops", "unfused: cuBLAS GEMM over T*B rows + bias kernel + snn_lif_fwd", fwd_flops, ms, "bf16")
-    ms = _time_graphed(lambda: torch.nn.functional.linear(xb.view(T * B, K), wb))
-    line("linear_fwd_tflops", "cuBLAS GEMM alone (no bias, no LIF), for scale", fwd_flops, ms, "bf16")
-
+    all_flops = 2.0 * T * B * K * M * 3
+    peak_tf, _ = bf16_peak_tflops()
     for dtype, name in ((torch.bfloat16, "bf16"), (torch.float32, "fp32 (TF32 off)")):
         x = (torch.rand((T, B, K), device=dev) < 0.2).to(dtype).requires_grad_(True)
         w = lin.weight.detach().clone().requires_grad_(True)
         b = lin.bias.detach().clone().requires_grad_(True)
         gs = torch.randn((T, B, M), device=dev).to(dtype)
-        for label, op in (("FcFire op (fused forward where supported)", lambda: sf.fc_fire_func(x, w, b)),
-                          ("fire_func(fc_func(x)) (library GEMM + LIF kernels)", lambda: sf.fire_func(sf.fc_func(x, w, b)))):
+        for label, op in (("FcFire op (tcgen05 kernels where supported; fp32 master weight cast per step)", lambda: sf.fc_fire_func(x, w, b)),
+                          ("fire_func(fc_func(x)) (library GEMMs + LIF kernels)", lambda: sf.fire_func(sf.fc_func(x, w, b)))):
             def step():
                 x.grad = w.grad = b.grad = None
                 op().backward(gs)
-            line("linear_lif_fwd_bwd_tflops", label, all_flops, _time_graphed(step), name)
+            ms = _time_graphed(step)
+            tf = all_flops / ms / 1e9
+            print(json.dumps({"metric": "linear_lif_fwd_bwd_tflops", "value": round(tf, 1), "unit": "TFLOP/s", "dtype": name,
+                              "ms": round(ms, 4), "frac_of_bf16_burst_peak": round(tf / peak_tf, 4),
+                              "config": {"workload": "fc 2048->2048 + LIF, T=8, batch %d" % B, "path": label}}))
 
 
 def main():
@@ -594,7 +752,9 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg")
     ap.add_argument("--batch", type=int, default=256, help="batch size of --workload linear_lif (a multiple of 32)")
-    ap.add_argument("--no-trainer", action="store_true", help="skip the spiking-CNN training leg")
+    ap.add_argument("--no-trainer", action="store_true", help="skip the spiking-CNN training legs")
+    ap.add_argument("--no-resnet", action="store_true", help="skip the ResNet-19-style training leg")
+    ap.add_argument("--no-linear-lif", action="store_true", help="skip the fused linear + LIF (tensor-core) leg")
     ap.add_argument("--trainer-steps", type=int, default=30)
     ap.add_argument("--log2n", type=int, default=26,
                     help="log2 of neurons per GPU (26 = the benchmark size; smaller only for profiler captures)")

@@ -247,7 +247,7 @@ int snn_linear_lif_error(int reset);
  *   SNN_F32) or NULL (skipped); grad_bias [M] fp32 or NULL (needs grad_weight);
  *   workspace: snn_linear_lif_bwd_workspace_bytes() bytes of device scratch, 256-byte aligned.
  * Supported when snn_linear_lif_bwd_supported() returns 1: SNN_BF16, 1 <= T <= 16, T*B >= 128,
- * K >= 64, M >= 128, K % 8 == 0, M % 8 == 0; otherwise SNN_ERR_UNSUPPORTED (use snn_lif_bwd and
+ * K >= 64, M >= 128, K % 64 == 0, M % 64 == 0; otherwise SNN_ERR_UNSUPPORTED (use snn_lif_bwd and
  * library GEMMs). Bounded waits report through snn_linear_lif_error() with codes 21 (producer),
  * 22 / 24 (MMA issuer), 23 (epilogue).
  */

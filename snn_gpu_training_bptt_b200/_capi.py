@@ -467,7 +467,7 @@ def linear_lif_bwd(x, weight, current, grad_spike, alpha, thresh, beta, interval
     in fp32. Entries that are not needed are None."""
     if not linear_lif_bwd_supported(x, weight):
         raise ValueError("linear_lif_bwd: unsupported problem (needs bf16, T <= 16, T*B >= 128, K >= 64, "
-                         "M >= 128, K % 8 == 0, M % 8 == 0)")
+                         "M >= 128, K % 64 == 0, M % 64 == 0)")
     if weight.dtype != torch.bfloat16 or current.dtype != torch.bfloat16:
         raise TypeError("linear_lif_bwd: weight and current must be bfloat16")
     if grad_weight_dtype not in (torch.float32, torch.bfloat16):

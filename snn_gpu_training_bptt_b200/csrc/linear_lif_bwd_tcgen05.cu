@@ -67,6 +67,8 @@ __device__ __forceinline__ void lif_du_body(const __nv_bfloat16* __restrict__ cu
     constexpr int RB = 256 / TX;           // batch items per block
     __shared__ float red[RB][128 + 4];
 
+    pdl_launch_dependents();
+    pdl_wait();                            // current / grad_spike come from the kernels before this one
     const int tx = threadIdx.x % TX, ty = threadIdx.x / TX;
     const int m = blockIdx.x * 128 + tx * VEC;
     const int b = blockIdx.y * RB + ty;
@@ -169,9 +171,9 @@ constexpr uint32_t kUnitBytes = TI * 128;                   // one staged output
 
 struct GemmProblem {
     CUtensorMap map_a;               // A operand (see a_mn)
-    CUtensorMap map_b;               // B operand, always MN-major: boxes {64 j, 64 r}
+    CUtensorMap map_b;               // B operand, always MN-major: box {64 j, 64 r, 4 groups of 64 j}
     CUtensorMap map_d;               // output [I][J], boxes {128 bytes of j, 128 i}, 128-byte swizzle
-    int a_mn;                        // 1: A is MN-major, boxes {64 i, 64 r}; 0: K-major, one box {64 r, 128 i}
+    int a_mn;                        // 1: A is MN-major, box {64 i, 64 r, 2 groups}; 0: K-major, box {64 r, 128 i}
     int out_f32;                     // output element type: 1 fp32 (32 columns per unit), 0 bf16 (64)
     int tiles_i, tiles_j, num_rb;    // tile grid and number of reduction stages
     int tile_begin;                  // first tile of this problem in the kernel's tile list
@@ -280,6 +282,7 @@ bwd_gemm_kernel(const __grid_constant__ GemmParams P)
     GemmStorage& sm = *reinterpret_cast<GemmStorage*>(
         (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    pdl_launch_dependents();
 
     if (threadIdx.x == 4 * 32) {
         for (int s = 0; s < GSTAGES; ++s) { mbar_init(&sm.full[s], 1); mbar_init(&sm.empty[s], 1); }
@@ -301,6 +304,7 @@ bwd_gemm_kernel(const __grid_constant__ GemmParams P)
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = sm.tmem_base;
+    pdl_wait();                                 // dU and the bias partials come from the kernel before this one
 
     if (warp == 4) {
         // ------------------------------ TMA producer ------------------------------
@@ -319,15 +323,11 @@ bwd_gemm_kernel(const __grid_constant__ GemmParams P)
                     const int r0 = rb * BR;
                     unsigned char* a = reinterpret_cast<unsigned char*>(sm.a[s]);
                     unsigned char* b = reinterpret_cast<unsigned char*>(sm.b[s]);
-                    if (pr.a_mn) {
-                        tma_load_2d(a, &pr.map_a, &sm.full[s], i0, r0);
-                        tma_load_2d(a + kBoxBytes, &pr.map_a, &sm.full[s], i0 + 64, r0);
-                    } else {
-                        tma_load_2d(a, &pr.map_a, &sm.full[s], r0, i0);
-                    }
-#pragma unroll
-                    for (int q = 0; q < TJ / 64; ++q)
-                        tma_load_2d(b + q * kBoxBytes, &pr.map_b, &sm.full[s], j0 + 64 * q, r0);
+                    // one TMA operation per operand: an MN-major tile is one 3-D box {64 elements, 64
+                    // reduction rows, groups of 64 elements}, which lands as consecutive 8 KB boxes
+                    if (pr.a_mn) tma_load_3d(a, &pr.map_a, &sm.full[s], 0, r0, i0 / 64);
+                    else tma_load_2d(a, &pr.map_a, &sm.full[s], r0, i0);
+                    tma_load_3d(b, &pr.map_b, &sm.full[s], 0, r0, j0 / 64);
                 }
             }
         }
@@ -339,7 +339,7 @@ bwd_gemm_kernel(const __grid_constant__ GemmParams P)
             for (int tile = blockIdx.x; tile < P.total_tiles && ok; tile += gridDim.x, ++local) {
                 const GemmProblem& pr = P.p[problem_of(P, tile)];
                 const bool a_mn = pr.a_mn != 0;
-                const uint32_t idesc = a_mn ? umma_idesc_bf16(TI, TJ, true, true) : umma_idesc_bf16(TI, TJ, false, true);
+                const uint32_t idesc = umma_idesc_bf16(TI, TJ, a_mn, true);
                 // per 16 reduction indices: a K-major tile advances 32 bytes inside its 128-byte rows,
                 // an MN-major tile advances 16 rows of 128 bytes (descriptor address unit = 16 bytes)
                 const uint32_t a_step = a_mn ? (16 * 128) >> 4 : 32 >> 4;
@@ -415,6 +415,177 @@ bwd_gemm_kernel(const __grid_constant__ GemmParams P)
     }
 }
 
+// ---------------------------------------------------------------------------------------------
+// CTA-pair variant: a cluster of two CTAs (the two SMs of a TPC) computes a 256 x 256 tile with
+// tcgen05.mma.cta_group::2. Each CTA stages its own 128 rows of A and HALF of the B tile (128 of
+// the 256 columns: two 64-column groups), so a CTA pulls 32 KB per stage for the flops that cost
+// the single-CTA kernel 48 KB: the single-CTA mainloop measured ~1.8x the tensor pipe's time per
+// stage waiting for operands, the pair's lower traffic is what removes that. Each CTA's tensor
+// memory receives its own 128 rows x 256 columns; both CTAs run the epilogue above on their rows.
+// Barriers as in the forward pair kernel: both CTAs' TMA loads complete on the LEADER's full
+// barrier (armed with the bytes of both), the leader's tcgen05.commit multicasts the stage-free /
+// accumulator-full arrivals to both CTAs, the epilogue threads of both CTAs arrive on the leader's
+// accumulator-empty barriers. No multicast loads. All waits bounded; the cluster barriers at entry
+// and exit are reached unconditionally by every thread of both CTAs.
+// ---------------------------------------------------------------------------------------------
+constexpr int GPSTAGES = 5;
+constexpr int PTI = 2 * TI;                                  // tile rows of a pair
+constexpr uint32_t kPairStageB = (TJ / 2) * BR * 2;          // 16 KB: this CTA's half of the B tile
+
+struct __align__(1024) GemmPairStorage {
+    __nv_bfloat16 a[GPSTAGES][TI * BR];
+    __nv_bfloat16 b[GPSTAGES][(TJ / 2) * BR];
+    unsigned char out[2][2][kUnitBytes];
+    uint64_t full[GPSTAGES];           // used in the leader
+    uint64_t empty[GPSTAGES];
+    uint64_t acc_full[2];
+    uint64_t acc_empty[2];             // used in the leader: 2 CTAs x 256 epilogue threads arrive
+    uint32_t tmem_base;
+    uint32_t epi_ok[2];
+};
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreadsG, 1)
+bwd_gemm_pair_kernel(const __grid_constant__ GemmParams P)
+{
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
+    GemmPairStorage& sm = *reinterpret_cast<GemmPairStorage*>(
+        (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_ctarank();
+    const bool leader = rank == 0;
+    const int pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
+    pdl_launch_dependents();
+
+    if (threadIdx.x == 4 * 32) {
+        for (int s = 0; s < GPSTAGES; ++s) { mbar_init(&sm.full[s], 1); mbar_init(&sm.empty[s], 1); }
+        for (int i = 0; i < 2; ++i) { mbar_init(&sm.acc_full[i], 1); mbar_init(&sm.acc_empty[i], 512); }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        for (int k = 0; k < P.count; ++k) {
+            asm volatile("prefetch.tensormap [%0];" ::"l"(&P.p[k].map_a) : "memory");
+            asm volatile("prefetch.tensormap [%0];" ::"l"(&P.p[k].map_b) : "memory");
+            asm volatile("prefetch.tensormap [%0];" ::"l"(&P.p[k].map_d) : "memory");
+        }
+    }
+    if (warp == 5) {
+        // one warp of each CTA of the pair takes part in the pair-wide allocation
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sm.tmem_base)),
+                     "r"(kTmemColsG)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    cluster_sync_all();                         // the peer's barriers are initialised past this point
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = sm.tmem_base;
+    pdl_wait();                                 // dU and the bias partials come from the kernel before this one
+
+    if (warp == 4) {
+        // ------------------------------ TMA producer (both CTAs) ------------------
+        if (lane == 0) {
+            int it = 0;
+            bool ok = true;
+            for (int tile = pair; tile < P.total_tiles && ok; tile += num_pairs) {
+                const GemmProblem& pr = P.p[problem_of(P, tile)];
+                const int local = tile - pr.tile_begin;
+                const int i0 = (local % pr.tiles_i) * PTI + static_cast<int>(rank) * TI;
+                const int j0 = (local / pr.tiles_i) * TJ + static_cast<int>(rank) * (TJ / 2);
+                for (int rb = 0; rb < pr.num_rb; ++rb, ++it) {
+                    const int s = it % GPSTAGES;
+                    const uint32_t parity = ((it / GPSTAGES) & 1) ^ 1;
+                    if (!mbar_wait(&sm.empty[s], parity)) { record_error(31); ok = false; break; }
+                    const uint32_t full_leader = mapa_shared(smem_u32(&sm.full[s]), 0);
+                    if (leader) mbar_expect_tx(&sm.full[s], 2 * (kStageA + kPairStageB));
+                    const int r0 = rb * BR;
+                    if (pr.a_mn) tma_load_3d_pair(sm.a[s], &pr.map_a, full_leader, 0, r0, i0 / 64);
+                    else tma_load_2d_pair(sm.a[s], &pr.map_a, full_leader, r0, i0);
+                    tma_load_3d_pair(sm.b[s], &pr.map_b, full_leader, 0, r0, j0 / 64);
+                }
+            }
+        }
+    } else if (warp == 5) {
+        // ------------------------------ MMA issuer (leader CTA only) --------------
+        if (lane == 0 && leader) {
+            int it = 0, local = 0;
+            bool ok = true;
+            for (int tile = pair; tile < P.total_tiles && ok; tile += num_pairs, ++local) {
+                const GemmProblem& pr = P.p[problem_of(P, tile)];
+                const bool a_mn = pr.a_mn != 0;
+                const uint32_t idesc = umma_idesc_bf16(PTI, TJ, a_mn, true);
+                const uint32_t a_step = a_mn ? (16 * 128) >> 4 : 32 >> 4;
+                constexpr uint32_t b_step = (16 * 128) >> 4;
+                const int buf = local & 1;
+                const uint32_t acc_parity = ((local >> 1) & 1) ^ 1;
+                if (!mbar_wait(&sm.acc_empty[buf], acc_parity)) { record_error(34); break; }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t tmem_acc = tmem_base + buf * TJ;
+                for (int rb = 0; rb < pr.num_rb; ++rb, ++it) {
+                    const int s = it % GPSTAGES;
+                    const uint32_t parity = (it / GPSTAGES) & 1;
+                    if (!mbar_wait(&sm.full[s], parity)) { record_error(32); ok = false; break; }
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const uint64_t da = a_mn ? umma_desc_sw128_mn(sm.a[s], kBoxBytes) : umma_desc_sw128(sm.a[s]);
+                    const uint64_t db = umma_desc_sw128_mn(sm.b[s], kBoxBytes);
+#pragma unroll
+                    for (int k = 0; k < BR / UMMA_K; ++k)
+                        umma_bf16_pair(tmem_acc, da + a_step * k, db + b_step * k, idesc, (rb | k) != 0 ? 1u : 0u);
+                    umma_commit_pair(&sm.empty[s]);
+                }
+                if (ok) umma_commit_pair(&sm.acc_full[buf]);
+            }
+        }
+    } else {
+        // ------------------------------ epilogue groups (both CTAs) ---------------
+        const int g = warp >= 6 ? 1 : 0;
+        const int quarter = warp & 3;
+        const int row = quarter * 32 + lane;
+        const bool elected = lane == 0 && warp == (g ? 6 : 0);
+        const uint32_t acc_empty_leader0 = mapa_shared(smem_u32(&sm.acc_empty[0]), 0);
+        const uint32_t acc_empty_leader1 = mapa_shared(smem_u32(&sm.acc_empty[1]), 0);
+        int local = 0, staged = 0;
+        for (int tile = pair; tile < P.total_tiles; tile += num_pairs, ++local) {
+            const GemmProblem& pr = P.p[problem_of(P, tile)];
+            const int tl = tile - pr.tile_begin;
+            const int i0 = (tl % pr.tiles_i) * PTI + static_cast<int>(rank) * TI;
+            const int j0 = (tl / pr.tiles_i) * TJ;
+            if (g == 0 && j0 == 0 && pr.grad_bias != nullptr && i0 + row < pr.rows) {
+                float s = 0.f;
+                for (int pz = 0; pz < pr.partial_rows; ++pz)
+                    s += pr.bias_partials[static_cast<long long>(pz) * pr.rows + i0 + row];
+                pr.grad_bias[i0 + row] = s;
+            }
+            const int buf = local & 1;
+            const uint32_t acc_parity = (local >> 1) & 1;
+            if (elected) {
+                const bool ok0 = mbar_wait(&sm.acc_full[buf], acc_parity);
+                if (!ok0) record_error(33);
+                sm.epi_ok[g] = ok0 ? 1u : 0u;
+            }
+            group_barrier(g);
+            if (sm.epi_ok[g] == 0u) break;
+            mbar_wait(&sm.acc_full[buf], acc_parity);     // already complete: orders this thread
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+
+            const uint32_t lane_base = tmem_base + buf * TJ + (static_cast<uint32_t>(quarter * 32) << 16);
+            const uint32_t acc_empty_leader = buf ? acc_empty_leader1 : acc_empty_leader0;
+            auto drained = [acc_empty_leader] { mbar_arrive_cluster(acc_empty_leader); };
+            if (pr.out_f32)
+                gemm_epilogue_tile<true>(sm.out[g], staged, g, elected, lane_base, row, &pr.map_d, i0, j0, drained);
+            else
+                gemm_epilogue_tile<false>(sm.out[g], staged, g, elected, lane_base, row, &pr.map_d, i0, j0, drained);
+        }
+        if (elected) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+    }
+
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    cluster_sync_all();                         // nobody touches the peer's memory or TMEM past this point
+    if (warp == 5) {
+        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemColsG)
+                     : "memory");
+    }
+}
+
 // ---- host side ---------------------------------------------------------------------------------
 inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
@@ -438,10 +609,9 @@ void launch_du(const void* cur, const void* gs, void* du, float* partials, int T
     constexpr int VEC = du_vec(TMAX);
     constexpr int RB = du_rows_per_block(TMAX);
     dim3 grid((M + 127) / 128, (B + RB - 1) / RB);
-    lif_du_kernel<TMAX, VEC><<<grid, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(cur),
-                                                   static_cast<const __nv_bfloat16*>(gs),
-                                                   static_cast<__nv_bfloat16*>(du), partials, T, B, M, alpha, thresh,
-                                                   beta, interval);
+    launch_pdl(lif_du_kernel<TMAX, VEC>, grid, dim3(256), 0, st, static_cast<const __nv_bfloat16*>(cur),
+               static_cast<const __nv_bfloat16*>(gs), static_cast<__nv_bfloat16*>(du), partials, T, B, M, alpha, thresh,
+               beta, interval);
 }
 
 bool map2d(CUtensorMap* out, const void* base, int64_t inner, int64_t outer, uint32_t box_inner, uint32_t box_outer,
@@ -450,6 +620,34 @@ bool map2d(CUtensorMap* out, const void* base, int64_t inner, int64_t outer, uin
     const cuuint64_t strides[1] = {static_cast<cuuint64_t>(inner) * (f32 ? 4 : 2)};
     const cuuint32_t box[2] = {box_inner, box_outer};
     return cached_map(out, base, 2, dims, strides, box, true, f32);
+}
+
+// A row-major [rows][cols] bf16 matrix seen as {64 columns, rows, cols / 64 column groups}: a box
+// {64, 64, groups} fetches a 64-row slab of `groups` adjacent 64-column groups and lays it out in
+// shared memory group after group, each group 64 rows of 128 bytes - the MN-major operand tile.
+bool map_mn(CUtensorMap* out, const void* base, int64_t cols, int64_t rows, uint32_t groups) {
+    const cuuint64_t dims[3] = {64, static_cast<cuuint64_t>(rows), static_cast<cuuint64_t>(cols / 64)};
+    const cuuint64_t strides[2] = {static_cast<cuuint64_t>(cols) * 2, 128};
+    const cuuint32_t box[3] = {64, 64, groups};
+    return cached_map(out, base, 3, dims, strides, box, true, false);
+}
+
+// SNN_LINEAR_LIF_BWD_VARIANT: 1 = single-CTA kernel (128 x 256 tiles), 2 = CTA-pair kernel
+// (256 x 256 tiles per pair); default 0 = the pair kernel whenever both GEMMs have at least 256
+// output rows (no half-empty pair tiles) and the device has SM pairs to run it.
+int bwd_variant() {
+    static int v = -1;
+    if (v < 0) {
+        const char* e = getenv("SNN_LINEAR_LIF_BWD_VARIANT");
+        v = (e != nullptr && e[0] >= '1' && e[0] <= '2') ? e[0] - '0' : 0;
+    }
+    return v;
+}
+bool use_pair_kernel(int64_t TB, int64_t M, int sms) {
+    if (sms < 2) return false;
+    if (bwd_variant() == 1) return false;
+    if (bwd_variant() == 2) return true;
+    return TB >= PTI && M >= PTI;
 }
 
 }  // namespace
@@ -473,7 +671,7 @@ int snn_linear_lif_bwd_supported(int64_t T, int64_t B, int64_t K, int64_t M, int
     if (dtype != SNN_BF16) return 0;
     if (T < 1 || T > 16 || B < 1) return 0;
     // TMA: row pitches are multiples of 16 bytes; boxes of 64 elements must fit the tensors
-    if (K < 64 || K % 8 != 0 || M < 128 || M % 8 != 0) return 0;
+    if (K < 64 || K % 64 != 0 || M < 128 || M % 64 != 0) return 0;
     if (T * B < 128 || T * B > INT32_MAX || K > INT32_MAX || M > INT32_MAX) return 0;
     return 1;
 }
@@ -516,12 +714,17 @@ int snn_linear_lif_bwd(const void* x, const void* weight, const void* current, c
     if (e != cudaSuccess) { snn_internal::set_last_cuda_error(static_cast<int>(e)); return SNN_ERR_CUDA; }
 
     const int64_t TB = T * B;
+    const int sms = sm_count();
+    if (sms <= 0) { snn_internal::set_last_cuda_error(static_cast<int>(cudaErrorInvalidDevice)); return SNN_ERR_CUDA; }
+    const bool pair = use_pair_kernel(TB, M, sms);
+    const int tile_rows = pair ? PTI : TI;
+    const uint32_t b_groups = pair ? TJ / 2 / 64 : TJ / 64;     // a pair member fetches half of the tile's columns
     GemmParams P;
     P.count = 0;
     P.total_tiles = 0;
     bool maps_ok = true;
     auto add = [&](GemmProblem& pr, int64_t I, int64_t J, int64_t R) {
-        pr.tiles_i = static_cast<int>((I + TI - 1) / TI);
+        pr.tiles_i = static_cast<int>((I + tile_rows - 1) / tile_rows);
         pr.tiles_j = static_cast<int>((J + TJ - 1) / TJ);
         pr.num_rb = static_cast<int>((R + BR - 1) / BR);
         pr.rows = static_cast<int>(I);
@@ -536,7 +739,7 @@ int snn_linear_lif_bwd(const void* x, const void* weight, const void* current, c
         pr.out_f32 = 0;
         pr.bias_partials = nullptr; pr.grad_bias = nullptr; pr.partial_rows = 0;
         maps_ok = maps_ok && map2d(&pr.map_a, du, M, TB, 64, TI);            // {64 m, 128 (t,b)}
-        maps_ok = maps_ok && map2d(&pr.map_b, weight, K, M, 64, 64);         // {64 k, 64 m}
+        maps_ok = maps_ok && map_mn(&pr.map_b, weight, K, M, b_groups);      // {64 k, 64 m, groups of k}
         maps_ok = maps_ok && map2d(&pr.map_d, grad_x, K, TB, 64, TI);        // {64 k = 128 bytes, 128 (t,b)}
         add(pr, TB, K, M);
     }
@@ -547,8 +750,8 @@ int snn_linear_lif_bwd(const void* x, const void* weight, const void* current, c
         pr.a_mn = 1;
         pr.out_f32 = f32 ? 1 : 0;
         pr.bias_partials = partials; pr.grad_bias = grad_bias; pr.partial_rows = ws.partial_rows;
-        maps_ok = maps_ok && map2d(&pr.map_a, du, M, TB, 64, 64);            // {64 m, 64 (t,b)}
-        maps_ok = maps_ok && map2d(&pr.map_b, x, K, TB, 64, 64);             // {64 k, 64 (t,b)}
+        maps_ok = maps_ok && map_mn(&pr.map_a, du, M, TB, TI / 64);          // {64 m, 64 (t,b), 2 groups of m}
+        maps_ok = maps_ok && map_mn(&pr.map_b, x, K, TB, b_groups);          // {64 k, 64 (t,b), groups of k}
         maps_ok = maps_ok && map2d(&pr.map_d, grad_weight, K, M, f32 ? 32 : 64, TI, f32);
         add(pr, M, K, TB);
     }
@@ -558,15 +761,22 @@ int snn_linear_lif_bwd(const void* x, const void* weight, const void* current, c
     }
     if (P.count == 0) return SNN_OK;
 
-    static_assert(sizeof(GemmStorage) + 1024 <= 227 * 1024, "shared memory budget");
-    const size_t smem = sizeof(GemmStorage) + 1024;
-    e = cudaFuncSetAttribute(bwd_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
-    const int sms = sm_count();
-    if (e == cudaSuccess && sms <= 0) e = cudaErrorInvalidDevice;
-    if (e != cudaSuccess) { snn_internal::set_last_cuda_error(static_cast<int>(e)); return SNN_ERR_CUDA; }
-    const int grid = P.total_tiles < sms ? P.total_tiles : sms;
-    bwd_gemm_kernel<<<grid, kThreadsG, smem, st>>>(P);
-    e = cudaGetLastError();
+    if (pair) {
+        static_assert(sizeof(GemmPairStorage) + 1024 <= 227 * 1024, "shared memory budget");
+        const size_t smem = sizeof(GemmPairStorage) + 1024;
+        e = cudaFuncSetAttribute(bwd_gemm_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+        if (e != cudaSuccess) { snn_internal::set_last_cuda_error(static_cast<int>(e)); return SNN_ERR_CUDA; }
+        const int pairs = P.total_tiles < sms / 2 ? P.total_tiles : sms / 2;
+        e = launch_pdl(bwd_gemm_pair_kernel, dim3(2 * pairs), dim3(kThreadsG), smem, st, P);
+    } else {
+        static_assert(sizeof(GemmStorage) + 1024 <= 227 * 1024, "shared memory budget");
+        const size_t smem = sizeof(GemmStorage) + 1024;
+        e = cudaFuncSetAttribute(bwd_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+        if (e != cudaSuccess) { snn_internal::set_last_cuda_error(static_cast<int>(e)); return SNN_ERR_CUDA; }
+        const int grid = P.total_tiles < sms ? P.total_tiles : sms;
+        e = launch_pdl(bwd_gemm_kernel, dim3(grid), dim3(kThreadsG), smem, st, P);
+    }
+    if (e == cudaSuccess) e = cudaGetLastError();
     if (e != cudaSuccess) { snn_internal::set_last_cuda_error(static_cast<int>(e)); return SNN_ERR_CUDA; }
     return SNN_OK;
 }

@@ -311,11 +311,15 @@ linear_lif_fwd_persistent_kernel(const __grid_constant__ CUtensorMap map_w, cons
     const int tiles_m = M / BM;
     const int num_tiles = tiles_m * (B / BT);
 
+    pdl_launch_dependents();
     int preloaded = 0;                          // K stages the producer thread has already requested
     if (threadIdx.x == 4 * 32) {
         for (int s = 0; s < PSTAGES; ++s) { mbar_init(&sm.full[s], 1); mbar_init(&sm.empty[s], 1); }
         for (int i = 0; i < 2; ++i) { mbar_init(&sm.acc_full[i], 1); mbar_init(&sm.acc_empty[i], 256); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_x) : "memory");
+        pdl_wait();                             // the loads below read what earlier kernels wrote
         // The first stages of the first tile need nothing but these barriers: request them now so
         // the TMEM allocation and the block-wide sync below overlap the first loads' latency.
         if (blockIdx.x < num_tiles) {
@@ -339,6 +343,7 @@ linear_lif_fwd_persistent_kernel(const __grid_constant__ CUtensorMap map_w, cons
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = sm.tmem_base;
+    pdl_wait();
 
     if (warp == 4) {
         // ------------------------------ TMA producer ------------------------------
@@ -468,56 +473,6 @@ struct __align__(1024) PairStorage {
     uint32_t epi_ok[2];
 };
 
-__device__ __forceinline__ uint32_t cluster_ctarank() {
-    uint32_t r;
-    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
-    return r;
-}
-// address of the same shared-memory location in the CTA of the given cluster rank
-__device__ __forceinline__ uint32_t mapa_shared(uint32_t addr, uint32_t rank) {
-    uint32_t r;
-    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
-    return r;
-}
-__device__ __forceinline__ void cluster_sync_all() {
-    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
-    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
-    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
-}
-__device__ __forceinline__ void tma_load_2d_pair(void* dst, const CUtensorMap* map, uint32_t bar_cluster_addr, int c0,
-                                                 int c1) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-        ::"r"(smem_u32(dst)), "l"(map), "r"(bar_cluster_addr), "r"(c0), "r"(c1)
-        : "memory");
-}
-__device__ __forceinline__ void tma_load_3d_pair(void* dst, const CUtensorMap* map, uint32_t bar_cluster_addr, int c0,
-                                                 int c1, int c2) {
-    asm volatile(
-        "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
-        ::"r"(smem_u32(dst)), "l"(map), "r"(bar_cluster_addr), "r"(c0), "r"(c1), "r"(c2)
-        : "memory");
-}
-__device__ __forceinline__ void umma_bf16_pair(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
-                                               uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5, %5, %5, %5, %5}, p;\n\t}"
-        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(0u)
-        : "memory");
-}
-// arrive on the barrier at this shared-memory offset in both CTAs of the pair once the MMAs issued so far retire
-__device__ __forceinline__ void umma_commit_pair(uint64_t* bar) {
-    const uint16_t mask = 3;
-    asm volatile(
-        "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
-        ::"r"(smem_u32(bar)), "h"(mask)
-        : "memory");
-}
-
 template <int T>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreadsP, 1)
 linear_lif_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
@@ -537,6 +492,7 @@ linear_lif_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
     const int pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
     const int num_kb = K / BK;
     const int tiles_m = M / (2 * BM);
+    pdl_launch_dependents();
     const int num_tiles = tiles_m * (B / BT);
 
     if (threadIdx.x == 4 * 32) {
@@ -559,6 +515,7 @@ linear_lif_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
     cluster_sync_all();                         // the peer's barriers are initialised past this point
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = sm.tmem_base;
+    pdl_wait();
 
     if (warp == 4) {
         // ------------------------------ TMA producer (both CTAs) ------------------
@@ -681,8 +638,9 @@ int launch_persistent(const CUtensorMap& mw, const CUtensorMap& mx, const CUtens
     if (e != cudaSuccess) { snn_internal::set_last_cuda_error(static_cast<int>(e)); return SNN_ERR_CUDA; }
     const int tiles = (M / BM) * (B / (WN / T));
     const int grid = tiles < sms ? tiles : sms;
-    kern<<<grid, kThreadsP, smem, st>>>(mw, mx, ms, mc, write_current, bias, B, K, M, alpha, thresh, t_real);
-    e = cudaGetLastError();
+    e = launch_pdl(kern, dim3(grid), dim3(kThreadsP), smem, st, mw, mx, ms, mc, write_current, bias, B, K, M, alpha,
+                   thresh, t_real);
+    if (e == cudaSuccess) e = cudaGetLastError();
     if (e != cudaSuccess) { snn_internal::set_last_cuda_error(static_cast<int>(e)); return SNN_ERR_CUDA; }
     return SNN_OK;
 }
@@ -700,8 +658,9 @@ int launch_pair(const CUtensorMap& mw, const CUtensorMap& mx, const CUtensorMap&
     if (e != cudaSuccess) { snn_internal::set_last_cuda_error(static_cast<int>(e)); return SNN_ERR_CUDA; }
     const int tiles = (M / (2 * BM)) * (B / (PAIR_N / T));
     const int pairs = tiles < sms / 2 ? tiles : sms / 2;
-    kern<<<2 * pairs, kThreadsP, smem, st>>>(mw, mx, ms, mc, write_current, bias, B, K, M, alpha, thresh, t_real);
-    e = cudaGetLastError();
+    e = launch_pdl(kern, dim3(2 * pairs), dim3(kThreadsP), smem, st, mw, mx, ms, mc, write_current, bias, B, K, M,
+                   alpha, thresh, t_real);
+    if (e == cudaSuccess) e = cudaGetLastError();
     if (e != cudaSuccess) { snn_internal::set_last_cuda_error(static_cast<int>(e)); return SNN_ERR_CUDA; }
     return SNN_OK;
 }

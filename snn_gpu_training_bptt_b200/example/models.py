@@ -39,9 +39,10 @@ class SpikingVGG(nn.Module):
     fc 8192->1024 - LIF - fc 1024->classes on the time-averaged spikes."""
 
     def __init__(self, time_steps=8, num_classes=10, act_dtype=torch.bfloat16, widths=(128, 256, 512),
-                 image=32, hidden=1024, fused_pool=True):
+                 image=32, hidden=1024, fused_pool=True, fused_fc=True):
         super().__init__()
         self.T, self.act_dtype = time_steps, act_dtype
+        self.fused_fc = fused_fc
         self.fused_pool = fused_pool and time_steps <= 16
         w1, w2, w3 = widths
         lif_pool = sop.FirePool if self.fused_pool else sop.Fire
@@ -55,7 +56,9 @@ class SpikingVGG(nn.Module):
         self.conv3_2 = sop.FireConv(w3, w3)
         self.fire3 = lif_pool()
         feat = w3 * (image // 8) ** 2
-        self.fc1 = sop.Fc(feat, hidden)
+        # fc1 + its LIF as one op (the tcgen05 linear + LIF kernels for bf16 activations); the
+        # parameters keep the names of an Fc layer either way
+        self.fc1 = sop.FcFire(feat, hidden) if fused_fc else sop.Fc(feat, hidden)
         self.fire_fc = sop.Fire()
         self.fc2 = nn.Linear(hidden, num_classes)
 
@@ -66,7 +69,7 @@ class SpikingVGG(nn.Module):
         x = pool(self.fire2(self.conv2_2(self.conv2_1(x))))
         x = pool(self.fire3(self.conv3_2(self.conv3_1(x))))
         x = x.reshape(x.shape[0], x.shape[1], -1)          # [T, B, C*H*W] in (C, H, W) order
-        x = self.fire_fc(self.fc1(x))
+        x = self.fc1(x) if self.fused_fc else self.fire_fc(self.fc1(x))
         return self.fc2(x.mean(dim=0).float())
 
 
@@ -93,9 +96,10 @@ class SpikingResNet19(nn.Module):
     channels (stride 2 between stages), global average pool, fc 512->256 - LIF - fc->classes."""
 
     def __init__(self, time_steps=16, num_classes=10, act_dtype=torch.bfloat16, widths=(128, 256, 512),
-                 blocks=(3, 3, 2), hidden=256):
+                 blocks=(3, 3, 2), hidden=256, fused_fc=True):
         super().__init__()
         self.T, self.act_dtype = time_steps, act_dtype
+        self.fused_fc = fused_fc
         self.stem = sop.Conv(3, widths[0])
         self.stem_fire = sop.Fire()
         layers, cin = [], widths[0]
@@ -104,7 +108,7 @@ class SpikingResNet19(nn.Module):
                 layers.append(_ResBlock(cin, w, 2 if (b == 0 and stage > 0) else 1))
                 cin = w
         self.blocks = nn.ModuleList(layers)
-        self.fc1 = sop.Fc(cin, hidden)
+        self.fc1 = sop.FcFire(cin, hidden) if fused_fc else sop.Fc(cin, hidden)
         self.fire_fc = sop.Fire()
         self.fc2 = nn.Linear(hidden, num_classes)
 
@@ -113,7 +117,7 @@ class SpikingResNet19(nn.Module):
         for blk in self.blocks:
             x = blk(x)
         x = x.mean(dim=(3, 4))                              # global average pool -> [T, B, C]
-        x = self.fire_fc(self.fc1(x))
+        x = self.fc1(x) if self.fused_fc else self.fire_fc(self.fc1(x))
         return self.fc2(x.mean(dim=0).float())
 
 

@@ -62,7 +62,7 @@ def load_checkpoint(path, model, optimizer=None):
 
 def run(model_name="vgg", time_steps=8, batch=64, steps=20, warmup=5, precision="bf16", lr=1e-2,
         bucket_mb=25.0, overlap=True, seed=0, log=False, checkpoint=None, graph=True,
-        return_params=False, model_kwargs=None):
+        return_params=False, model_kwargs=None, communicate=True):
     """Trains for warmup+steps steps; returns a dict with samples/sec (whole job) and timings.
 
     ``graph=True`` captures one whole training step (zero_grad, forward, loss, backward with its
@@ -83,7 +83,7 @@ def run(model_name="vgg", time_steps=8, batch=64, steps=20, warmup=5, precision=
     torch.backends.cudnn.benchmark = True
     torch.manual_seed(seed)
     net = models.build(model_name, time_steps=time_steps, act_dtype=act_dtype, **(model_kwargs or {})).to(dev)
-    model = DistributedDataParallel(net, bucket_mb=bucket_mb, overlap=overlap)
+    model = DistributedDataParallel(net, bucket_mb=bucket_mb, overlap=overlap, communicate=communicate)
     opt = torch.optim.SGD(net.parameters(), lr=lr, momentum=0.9)
     data = SyntheticImages(batch, seed=1000 + rank)
     n_params = sum(p.numel() for p in net.parameters())
@@ -161,6 +161,8 @@ def run(model_name="vgg", time_steps=8, batch=64, steps=20, warmup=5, precision=
         "samples_per_s_wall": batch * world * steps / wall, "final_loss": final_loss,
         "h2d_bytes_per_step": data.bytes_per_batch, "d2h_bytes_per_step": 4,
         "grad_buckets": len(model.buckets), "overlap": overlap, "cuda_graph": bool(graph),
+        "bucket_bytes": [b["flat"].numel() * b["flat"].element_size() for b in model.buckets],
+        "communicate": communicate,
     }
     if return_params:
         out["params"] = [p.detach().float().cpu() for p in net.parameters()]

@@ -172,9 +172,9 @@ def _bwd_through_capi(capi, x, w, current, gs, gw_dtype, want_gx=True, want_gb=T
     return gx, gw, gb, du
 
 
-# ragged sizes on purpose: row counts that are not multiples of the 128 x 256 tiles, K / M that are
-# only multiples of 8, T = 1 and T values between the compiled step counts
-BWD_SHAPES = SHAPES + [(8, 40, 72, 136), (1, 128, 64, 128), (7, 24, 200, 328), (3, 100, 1000, 520)]
+# ragged sizes on purpose: row counts and K / M that are not multiples of the 128 x 256 tiles (K and M
+# only multiples of 64), T = 1 and T values between the compiled step counts
+BWD_SHAPES = SHAPES + [(8, 40, 192, 320), (1, 128, 64, 128), (7, 24, 320, 448), (3, 100, 960, 576)]
 
 
 @pytest.mark.parametrize("shape", BWD_SHAPES)
@@ -202,6 +202,22 @@ def test_fused_backward_against_oracle_and_fp32_gemms(capi, shape):
         assert float((gb.double() - want_gb).abs().max()) <= 1e-5 * float(d.abs().sum(dim=0).max() + 1e-6)
 
 
+@pytest.mark.parametrize("variant", ["1", "2"])
+def test_each_backward_kernel_variant_passes_the_backward_checks(capi, variant):
+    """The library picks the single-CTA (1) or the CTA-pair (2) gradient-GEMM kernel per problem; the
+    environment switch forces one for every shape, including those where a pair tile is half empty.
+    It is read once per process, so each forced variant runs in a child process."""
+    if os.environ.get("SNN_LINEAR_LIF_BWD_VARIANT"):
+        pytest.skip("already inside a forced-variant run")
+    env = dict(os.environ, SNN_LINEAR_LIF_BWD_VARIANT=variant)
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    out = subprocess.run([sys.executable, "-m", "pytest", "-x", "-q", "-m", "gpu", "-p", "no:cacheprovider",
+                          os.path.join("tests", "test_linear_lif_gpu.py"), "-k", "fused_backward_against"],
+                         cwd=root, env=env, capture_output=True, text=True, timeout=600)
+    assert out.returncode == 0, out.stdout[-2000:] + out.stderr[-2000:]
+    assert "%d passed" % len(BWD_SHAPES) in out.stdout, out.stdout[-500:]
+
+
 def test_fused_backward_optional_outputs_and_errors(capi):
     import ctypes
     T, B, K, M = 8, 32, 128, 256
@@ -223,7 +239,7 @@ def test_fused_backward_optional_outputs_and_errors(capi):
                          kw.get("K", K), M, kw.get("dtype", 1), 0, A, TH, 1.0, 0.5, P(ws), kw.get("need", need), None]
     assert L.snn_linear_lif_bwd(*args(need=need - 1)) == 6          # workspace too small
     assert L.snn_linear_lif_bwd(*args(T=17)) == 5                   # beyond the register-resident time axis
-    assert L.snn_linear_lif_bwd(*args(K=60)) == 5
+    assert L.snn_linear_lif_bwd(*args(K=96)) == 5
     assert L.snn_linear_lif_bwd(*args(dtype=0)) == 5                # fp32 operands are not served
     assert L.snn_linear_lif_bwd(*args(x=None)) == 1
     assert L.snn_linear_lif_bwd_workspace_bytes(17, B, K, M, 1) < 0
