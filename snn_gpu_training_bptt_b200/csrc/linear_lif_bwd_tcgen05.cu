@@ -169,6 +169,10 @@ constexpr uint32_t kStageB = TJ * BR * 2;                   // 32 KB
 constexpr uint32_t kTmemColsG = 2 * TJ;                     // two accumulators = all of tensor memory
 constexpr uint32_t kUnitBytes = TI * 128;                   // one staged output unit: 128 rows of 128 bytes
 
+#ifdef SNN_TC_STAMPS
+__device__ int g_stamp_debug = 0;
+#endif
+
 struct GemmProblem {
     CUtensorMap map_a;               // A operand (see a_mn)
     CUtensorMap map_b;               // B operand, always MN-major: box {64 j, 64 r, 4 groups of 64 j}
@@ -228,8 +232,11 @@ __device__ __forceinline__ int problem_of(const GemmParams& P, int tile) {
 // buffers as rows of 128 bytes whose 16-byte chunks are XOR-swizzled with (row & 7) - the layout
 // a 128-byte-swizzle tensor map expects - so the eight lanes that write chunk c of eight
 // consecutive rows hit eight different bank groups.
-template <bool F32, typename Drained>
-__device__ __forceinline__ void gemm_epilogue_tile(unsigned char (&stage)[2][kUnitBytes], int& k, int g, bool elected,
+// NBUF staging buffers per group: a TMA store takes ~1000 cycles to read its 16 KB out of shared
+// memory, longer than a unit's arithmetic, so with NBUF buffers up to NBUF - 1 stores are in flight
+// while the next unit is being staged.
+template <bool F32, int NBUF, typename Drained>
+__device__ __forceinline__ void gemm_epilogue_tile(unsigned char (&stage)[NBUF][kUnitBytes], int& k, int g, bool elected,
                                                    uint32_t lane_base, int row, const CUtensorMap* map_d, int i0,
                                                    int j0, Drained&& drained)
 {
@@ -238,6 +245,8 @@ __device__ __forceinline__ void gemm_epilogue_tile(unsigned char (&stage)[2][kUn
 #pragma unroll 1
     for (int u = 0; u < PER_GROUP; ++u) {
         const int q = g + 2 * u;
+        const bool stamp = elected && g == 0 && u < 2;
+        if (stamp) SNN_TC_STAMP(56 + 4 * u);
         uint32_t r[UC / 32][32];
         tmem_ld32(lane_base + q * UC, r[0]);
         if (!F32) tmem_ld32(lane_base + q * UC + 32, r[UC / 32 - 1]);
@@ -245,10 +254,13 @@ __device__ __forceinline__ void gemm_epilogue_tile(unsigned char (&stage)[2][kUn
         tmem_ld_wait32(r[0]);
         if (!F32) tmem_ld_wait32(r[UC / 32 - 1]);
         if (u + 1 == PER_GROUP) {
+            if (stamp) SNN_TC_STAMP(6);
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             drained();                          // last TMEM read of this tile done: give the buffer back
+            if (stamp) SNN_TC_STAMP(7);
         }
-        unsigned char* st = stage[k & 1];
+        if (stamp) SNN_TC_STAMP(57 + 4 * u);
+        unsigned char* st = stage[k % NBUF];
         uint4* rowp = reinterpret_cast<uint4*>(st + row * 128);
 #pragma unroll
         for (int c = 0; c < 8; ++c) {
@@ -262,14 +274,18 @@ __device__ __forceinline__ void gemm_epilogue_tile(unsigned char (&stage)[2][kUn
             }
             rowp[c ^ (row & 7)] = v;
         }
+        if (stamp) SNN_TC_STAMP(58 + 4 * u);
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-        // the other buffer's store (issued one unit ago) must have been read out of shared memory
-        // before anybody passes the barrier and starts writing the next unit into it
-        if (elected) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+        // the next unit goes into the buffer whose store was issued NBUF - 1 units ago: that store
+        // must have been read out of shared memory before anybody passes the barrier (the store
+        // of this unit is not issued yet, so "all but the latest NBUF - 2" covers it)
+        if (elected) asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(NBUF - 2) : "memory");
         group_barrier(g);
+        if (stamp) SNN_TC_STAMP(59 + 4 * u);
         if (elected) {
             tma_store_2d(map_d, st, j0 + q * UC, i0);
             asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+            if (stamp && u == 0) SNN_TC_STAMP(48);
         }
         ++k;
     }
@@ -399,9 +415,9 @@ bwd_gemm_kernel(const __grid_constant__ GemmParams P)
             uint64_t* drained_bar = &sm.acc_empty[buf];
             auto drained = [drained_bar] { mbar_arrive(drained_bar); };
             if (pr.out_f32)
-                gemm_epilogue_tile<true>(sm.out[g], staged, g, elected, lane_base, row, &pr.map_d, i0, j0, drained);
+                gemm_epilogue_tile<true, 2>(sm.out[g], staged, g, elected, lane_base, row, &pr.map_d, i0, j0, drained);
             else
-                gemm_epilogue_tile<false>(sm.out[g], staged, g, elected, lane_base, row, &pr.map_d, i0, j0, drained);
+                gemm_epilogue_tile<false, 2>(sm.out[g], staged, g, elected, lane_base, row, &pr.map_d, i0, j0, drained);
         }
         // shared memory must outlive the reads of the last stores
         if (elected) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
@@ -428,14 +444,15 @@ bwd_gemm_kernel(const __grid_constant__ GemmParams P)
 // accumulator-empty barriers. No multicast loads. All waits bounded; the cluster barriers at entry
 // and exit are reached unconditionally by every thread of both CTAs.
 // ---------------------------------------------------------------------------------------------
-constexpr int GPSTAGES = 5;
+constexpr int GPSTAGES = 5;                                  // 5 x 32 KB in flight (4 measured ~12 % slower on a CTA's second tile)
+constexpr int kPairOutBufs = 2;                              // output staging buffers per epilogue group
 constexpr int PTI = 2 * TI;                                  // tile rows of a pair
 constexpr uint32_t kPairStageB = (TJ / 2) * BR * 2;          // 16 KB: this CTA's half of the B tile
 
 struct __align__(1024) GemmPairStorage {
     __nv_bfloat16 a[GPSTAGES][TI * BR];
     __nv_bfloat16 b[GPSTAGES][(TJ / 2) * BR];
-    unsigned char out[2][2][kUnitBytes];
+    unsigned char out[2][kPairOutBufs][kUnitBytes];
     uint64_t full[GPSTAGES];           // used in the leader
     uint64_t empty[GPSTAGES];
     uint64_t acc_full[2];
@@ -454,6 +471,7 @@ bwd_gemm_pair_kernel(const __grid_constant__ GemmParams P)
     const uint32_t rank = cluster_ctarank();
     const bool leader = rank == 0;
     const int pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
+    if (threadIdx.x == 0) SNN_TC_STAMP(0);
     pdl_launch_dependents();
 
     if (threadIdx.x == 4 * 32) {
@@ -478,7 +496,9 @@ bwd_gemm_pair_kernel(const __grid_constant__ GemmParams P)
     cluster_sync_all();                         // the peer's barriers are initialised past this point
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = sm.tmem_base;
+    if (threadIdx.x == 0) SNN_TC_STAMP(1);
     pdl_wait();                                 // dU and the bias partials come from the kernel before this one
+    if (threadIdx.x == 0) SNN_TC_STAMP(2);
 
     if (warp == 4) {
         // ------------------------------ TMA producer (both CTAs) ------------------
@@ -511,7 +531,12 @@ bwd_gemm_pair_kernel(const __grid_constant__ GemmParams P)
             for (int tile = pair; tile < P.total_tiles && ok; tile += num_pairs, ++local) {
                 const GemmProblem& pr = P.p[problem_of(P, tile)];
                 const bool a_mn = pr.a_mn != 0;
-                const uint32_t idesc = umma_idesc_bf16(PTI, TJ, a_mn, true);
+#ifdef SNN_TC_STAMPS
+                const bool b_mn = g_stamp_debug == 0;      // timing experiment: read B as if it were K-major
+#else
+                constexpr bool b_mn = true;
+#endif
+                const uint32_t idesc = umma_idesc_bf16(PTI, TJ, a_mn, b_mn);
                 const uint32_t a_step = a_mn ? (16 * 128) >> 4 : 32 >> 4;
                 constexpr uint32_t b_step = (16 * 128) >> 4;
                 const int buf = local & 1;
@@ -524,14 +549,17 @@ bwd_gemm_pair_kernel(const __grid_constant__ GemmParams P)
                     const uint32_t parity = (it / GPSTAGES) & 1;
                     if (!mbar_wait(&sm.full[s], parity)) { record_error(32); ok = false; break; }
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    if (it < 40) SNN_TC_STAMP(8 + it);
                     const uint64_t da = a_mn ? umma_desc_sw128_mn(sm.a[s], kBoxBytes) : umma_desc_sw128(sm.a[s]);
-                    const uint64_t db = umma_desc_sw128_mn(sm.b[s], kBoxBytes);
+                    const uint64_t db = b_mn ? umma_desc_sw128_mn(sm.b[s], kBoxBytes) : umma_desc_sw128(sm.b[s]);
+                    const uint32_t b_adv = b_mn ? b_step : 2u;
 #pragma unroll
                     for (int k = 0; k < BR / UMMA_K; ++k)
-                        umma_bf16_pair(tmem_acc, da + a_step * k, db + b_step * k, idesc, (rb | k) != 0 ? 1u : 0u);
+                        umma_bf16_pair(tmem_acc, da + a_step * k, db + b_adv * k, idesc, (rb | k) != 0 ? 1u : 0u);
                     umma_commit_pair(&sm.empty[s]);
                 }
                 if (ok) umma_commit_pair(&sm.acc_full[buf]);
+                if (local < 2) SNN_TC_STAMP(3 + local);
             }
         }
     } else {
@@ -565,16 +593,19 @@ bwd_gemm_pair_kernel(const __grid_constant__ GemmParams P)
             if (sm.epi_ok[g] == 0u) break;
             mbar_wait(&sm.acc_full[buf], acc_parity);     // already complete: orders this thread
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            if (elected && g == 0 && local < 2) SNN_TC_STAMP(50 + 2 * local);
 
             const uint32_t lane_base = tmem_base + buf * TJ + (static_cast<uint32_t>(quarter * 32) << 16);
             const uint32_t acc_empty_leader = buf ? acc_empty_leader1 : acc_empty_leader0;
             auto drained = [acc_empty_leader] { mbar_arrive_cluster(acc_empty_leader); };
             if (pr.out_f32)
-                gemm_epilogue_tile<true>(sm.out[g], staged, g, elected, lane_base, row, &pr.map_d, i0, j0, drained);
+                gemm_epilogue_tile<true, kPairOutBufs>(sm.out[g], staged, g, elected, lane_base, row, &pr.map_d, i0, j0, drained);
             else
-                gemm_epilogue_tile<false>(sm.out[g], staged, g, elected, lane_base, row, &pr.map_d, i0, j0, drained);
+                gemm_epilogue_tile<false, kPairOutBufs>(sm.out[g], staged, g, elected, lane_base, row, &pr.map_d, i0, j0, drained);
+            if (elected && g == 0 && local < 2) SNN_TC_STAMP(51 + 2 * local);
         }
         if (elected) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+        if (elected && g == 0) SNN_TC_STAMP(5);
     }
 
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -667,6 +698,12 @@ int linear_lif_bwd_error(int reset) {
 
 extern "C" {
 
+#ifdef SNN_TC_STAMPS
+int snn_tc_stamps_read(long long* out, int ctas) {   // stamp builds only
+    return cudaMemcpyFromSymbol(out, snn_tc::g_tc_stamps, sizeof(long long) * 64 * ctas) == cudaSuccess ? 0 : 7;
+}
+#endif
+
 int snn_linear_lif_bwd_supported(int64_t T, int64_t B, int64_t K, int64_t M, int dtype) {
     if (dtype != SNN_BF16) return 0;
     if (T < 1 || T > 16 || B < 1) return 0;
@@ -732,17 +769,8 @@ int snn_linear_lif_bwd(const void* x, const void* weight, const void* current, c
         P.total_tiles += pr.tiles_i * pr.tiles_j;
         ++P.count;
     };
-    if (grad_x != nullptr) {
-        // grad_x[(t,b), k] = sum_m dU[(t,b), m] W[m, k]
-        GemmProblem& pr = P.p[P.count];
-        pr.a_mn = 0;
-        pr.out_f32 = 0;
-        pr.bias_partials = nullptr; pr.grad_bias = nullptr; pr.partial_rows = 0;
-        maps_ok = maps_ok && map2d(&pr.map_a, du, M, TB, 64, TI);            // {64 m, 128 (t,b)}
-        maps_ok = maps_ok && map_mn(&pr.map_b, weight, K, M, b_groups);      // {64 k, 64 m, groups of k}
-        maps_ok = maps_ok && map2d(&pr.map_d, grad_x, K, TB, 64, TI);        // {64 k = 128 bytes, 128 (t,b)}
-        add(pr, TB, K, M);
-    }
+    // The weight-gradient tiles go first: the last round's epilogue is exposed, and the input
+    // gradient writes half as many bytes per tile (bf16 against fp32).
     if (grad_weight != nullptr) {
         // grad_W[m, k] = sum_(t,b) dU[(t,b), m] x[(t,b), k]
         GemmProblem& pr = P.p[P.count];
@@ -754,6 +782,17 @@ int snn_linear_lif_bwd(const void* x, const void* weight, const void* current, c
         maps_ok = maps_ok && map_mn(&pr.map_b, x, K, TB, b_groups);          // {64 k, 64 (t,b), groups of k}
         maps_ok = maps_ok && map2d(&pr.map_d, grad_weight, K, M, f32 ? 32 : 64, TI, f32);
         add(pr, M, K, TB);
+    }
+    if (grad_x != nullptr) {
+        // grad_x[(t,b), k] = sum_m dU[(t,b), m] W[m, k]
+        GemmProblem& pr = P.p[P.count];
+        pr.a_mn = 0;
+        pr.out_f32 = 0;
+        pr.bias_partials = nullptr; pr.grad_bias = nullptr; pr.partial_rows = 0;
+        maps_ok = maps_ok && map2d(&pr.map_a, du, M, TB, 64, TI);            // {64 m, 128 (t,b)}
+        maps_ok = maps_ok && map_mn(&pr.map_b, weight, K, M, b_groups);      // {64 k, 64 m, groups of k}
+        maps_ok = maps_ok && map2d(&pr.map_d, grad_x, K, TB, 64, TI);        // {64 k = 128 bytes, 128 (t,b)}
+        add(pr, TB, K, M);
     }
     if (!maps_ok) {
         snn_internal::set_last_cuda_error(static_cast<int>(cudaErrorInvalidValue));
