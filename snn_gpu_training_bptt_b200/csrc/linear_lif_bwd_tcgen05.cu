@@ -169,10 +169,6 @@ constexpr uint32_t kStageB = TJ * BR * 2;                   // 32 KB
 constexpr uint32_t kTmemColsG = 2 * TJ;                     // two accumulators = all of tensor memory
 constexpr uint32_t kUnitBytes = TI * 128;                   // one staged output unit: 128 rows of 128 bytes
 
-#ifdef SNN_TC_STAMPS
-__device__ int g_stamp_debug = 0;
-#endif
-
 struct GemmProblem {
     CUtensorMap map_a;               // A operand (see a_mn)
     CUtensorMap map_b;               // B operand, always MN-major: box {64 j, 64 r, 4 groups of 64 j}
@@ -298,6 +294,7 @@ bwd_gemm_kernel(const __grid_constant__ GemmParams P)
     GemmStorage& sm = *reinterpret_cast<GemmStorage*>(
         (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) SNN_TC_STAMP(0);
     pdl_launch_dependents();
 
     if (threadIdx.x == 4 * 32) {
@@ -320,7 +317,9 @@ bwd_gemm_kernel(const __grid_constant__ GemmParams P)
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = sm.tmem_base;
+    if (threadIdx.x == 0) SNN_TC_STAMP(1);
     pdl_wait();                                 // dU and the bias partials come from the kernel before this one
+    if (threadIdx.x == 0) SNN_TC_STAMP(2);
 
     if (warp == 4) {
         // ------------------------------ TMA producer ------------------------------
@@ -370,6 +369,7 @@ bwd_gemm_kernel(const __grid_constant__ GemmParams P)
                     const uint32_t parity = (it / GSTAGES) & 1;
                     if (!mbar_wait(&sm.full[s], parity)) { record_error(22); ok = false; break; }
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    if (it < 40) SNN_TC_STAMP(8 + it);
                     const uint64_t da = a_mn ? umma_desc_sw128_mn(sm.a[s], kBoxBytes) : umma_desc_sw128(sm.a[s]);
                     const uint64_t db = umma_desc_sw128_mn(sm.b[s], kBoxBytes);
 #pragma unroll
@@ -378,6 +378,7 @@ bwd_gemm_kernel(const __grid_constant__ GemmParams P)
                     umma_commit(&sm.empty[s]);        // stage reusable once these MMAs have read it
                 }
                 if (ok) umma_commit(&sm.acc_full[buf]);
+                if (local < 2) SNN_TC_STAMP(3 + local);
             }
         }
     } else {
@@ -410,6 +411,7 @@ bwd_gemm_kernel(const __grid_constant__ GemmParams P)
             if (sm.epi_ok[g] == 0u) break;
             mbar_wait(&sm.acc_full[buf], acc_parity);     // already complete: returns at once, orders this thread
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            if (elected && g == 0 && local < 2) SNN_TC_STAMP(50 + 2 * local);
 
             const uint32_t lane_base = tmem_base + buf * TJ + (static_cast<uint32_t>(quarter * 32) << 16);
             uint64_t* drained_bar = &sm.acc_empty[buf];
@@ -418,9 +420,11 @@ bwd_gemm_kernel(const __grid_constant__ GemmParams P)
                 gemm_epilogue_tile<true, 2>(sm.out[g], staged, g, elected, lane_base, row, &pr.map_d, i0, j0, drained);
             else
                 gemm_epilogue_tile<false, 2>(sm.out[g], staged, g, elected, lane_base, row, &pr.map_d, i0, j0, drained);
+            if (elected && g == 0 && local < 2) SNN_TC_STAMP(51 + 2 * local);
         }
         // shared memory must outlive the reads of the last stores
         if (elected) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+        if (elected && g == 0) SNN_TC_STAMP(5);
     }
 
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -435,8 +439,11 @@ bwd_gemm_kernel(const __grid_constant__ GemmParams P)
 // CTA-pair variant: a cluster of two CTAs (the two SMs of a TPC) computes a 256 x 256 tile with
 // tcgen05.mma.cta_group::2. Each CTA stages its own 128 rows of A and HALF of the B tile (128 of
 // the 256 columns: two 64-column groups), so a CTA pulls 32 KB per stage for the flops that cost
-// the single-CTA kernel 48 KB: the single-CTA mainloop measured ~1.8x the tensor pipe's time per
-// stage waiting for operands, the pair's lower traffic is what removes that. Each CTA's tensor
+// the single-CTA kernel 48 KB. Measured with cycle stamps at T=8, batch 256, 2048 -> 2048: the pair's
+// K stage (four 256 x 256 x 16 MMAs) takes a steady 610-640 cycles whether or not operands are
+// waited for - the tensor pipe's own rate for this instruction shape - while the single-CTA
+// kernel's stages (590 cycles on a CTA's first tile) stretch to 700-1500 on its second tile, when
+// the epilogue's stores compete for L2; with many tiles per CTA the pair is ~20 % faster. Each CTA's tensor
 // memory receives its own 128 rows x 256 columns; both CTAs run the epilogue above on their rows.
 // Barriers as in the forward pair kernel: both CTAs' TMA loads complete on the LEADER's full
 // barrier (armed with the bytes of both), the leader's tcgen05.commit multicasts the stage-free /
@@ -531,12 +538,7 @@ bwd_gemm_pair_kernel(const __grid_constant__ GemmParams P)
             for (int tile = pair; tile < P.total_tiles && ok; tile += num_pairs, ++local) {
                 const GemmProblem& pr = P.p[problem_of(P, tile)];
                 const bool a_mn = pr.a_mn != 0;
-#ifdef SNN_TC_STAMPS
-                const bool b_mn = g_stamp_debug == 0;      // timing experiment: read B as if it were K-major
-#else
-                constexpr bool b_mn = true;
-#endif
-                const uint32_t idesc = umma_idesc_bf16(PTI, TJ, a_mn, b_mn);
+                const uint32_t idesc = umma_idesc_bf16(PTI, TJ, a_mn, true);
                 const uint32_t a_step = a_mn ? (16 * 128) >> 4 : 32 >> 4;
                 constexpr uint32_t b_step = (16 * 128) >> 4;
                 const int buf = local & 1;
@@ -551,11 +553,10 @@ bwd_gemm_pair_kernel(const __grid_constant__ GemmParams P)
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                     if (it < 40) SNN_TC_STAMP(8 + it);
                     const uint64_t da = a_mn ? umma_desc_sw128_mn(sm.a[s], kBoxBytes) : umma_desc_sw128(sm.a[s]);
-                    const uint64_t db = b_mn ? umma_desc_sw128_mn(sm.b[s], kBoxBytes) : umma_desc_sw128(sm.b[s]);
-                    const uint32_t b_adv = b_mn ? b_step : 2u;
+                    const uint64_t db = umma_desc_sw128_mn(sm.b[s], kBoxBytes);
 #pragma unroll
                     for (int k = 0; k < BR / UMMA_K; ++k)
-                        umma_bf16_pair(tmem_acc, da + a_step * k, db + b_adv * k, idesc, (rb | k) != 0 ? 1u : 0u);
+                        umma_bf16_pair(tmem_acc, da + a_step * k, db + b_step * k, idesc, (rb | k) != 0 ? 1u : 0u);
                     umma_commit_pair(&sm.empty[s]);
                 }
                 if (ok) umma_commit_pair(&sm.acc_full[buf]);
