@@ -366,7 +366,7 @@ def run_ours(args):
                "h2d_bytes_per_step": pipe.h2d_bytes, "d2h_bytes_per_step": pipe.d2h_bytes,
                "ms_per_step": round(dt * 1e3, 3), "neurons_per_gpu": n_e2e,
                "launches_per_step": pipe.launches_per_run, "matches_device_run": same,
-               "how": "pinned host x,grad -> 3-stream chunked H2D / snn_lif_fwd / snn_lif_bwd / D2H of spike,grad_x",
+               "how": "pinned host x,grad -> 3-stream chunked H2D (one pitched copy per [T, chunk] slab) / snn_lif_fwd / snn_lif_bwd / D2H of spike,grad_x",
                "host_link": {"copy_only_ms": round(copy_ms, 3),
                              "gbs_each_way": round(pipe.h2d_bytes / copy_ms / 1e6, 2),
                              "frac": round(copy_ms / (dt * 1e3), 4),
@@ -395,7 +395,8 @@ def run_ours(args):
         from snn_gpu_training_bptt_b200.example import train_synthetic
 
         def trainer_leg(name, time_steps, batch, steps, workload):
-            tr = train_synthetic.run(name, time_steps=time_steps, batch=batch, steps=steps, warmup=5, precision="bf16")
+            tr = train_synthetic.run(name, time_steps=time_steps, batch=batch, steps=steps, warmup=5, precision="bf16",
+                                     bucket_mb=args.bucket_mb)
             leg = {"metric": "spiking_cnn_train_samples_per_s", "value": round(tr["samples_per_s"], 1),
                    "unit": "samples/s", "ms_per_step": round(tr["ms_per_step"], 3),
                    "config": {"workload": workload,
@@ -407,7 +408,7 @@ def run_ours(args):
                 # the same captured step with the all-reduces left out: the difference is the
                 # communication time that backward does not hide
                 quiet = train_synthetic.run(name, time_steps=time_steps, batch=batch, steps=steps, warmup=5,
-                                            precision="bf16", communicate=False)
+                                            precision="bf16", communicate=False, bucket_mb=args.bucket_mb)
                 leg["ms_per_step_without_allreduce"] = round(quiet["ms_per_step"], 3)
                 leg["exposed_comm_ms"] = round(tr["ms_per_step"] - quiet["ms_per_step"], 3)
             return leg
@@ -505,12 +506,14 @@ def _time_kernel(fn, reps, flush=None):
     return statistics.median(times)
 
 
-def _host_link_copy_ms(hx, hg, hs, hgx, dev, reps=2):
+def _host_link_copy_ms(hx, hg, hs, hgx, dev, reps=2, chunk=1 << 22, pitched=True):
     """Time of moving one end-to-end step's bytes over the host link and nothing else: the pinned
-    inputs H2D on one stream while as many bytes go D2H into the pinned outputs on another."""
+    inputs H2D on one stream while as many bytes go D2H into the pinned outputs on another.
+    pitched = one transfer per [T, chunk] slab (as the pipeline copies), else T row copies."""
     import torch
+    from snn_gpu_training_bptt_b200 import _capi
     T, n = hx.shape
-    chunk = min(n, 1 << 22)
+    chunk = min(n, chunk)
     up, down = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
     stage_in = torch.empty((2, T, chunk), dtype=hx.dtype, device=dev)
     stage_out = torch.zeros((2, T, chunk), dtype=hx.dtype, device=dev)
@@ -520,17 +523,88 @@ def _host_link_copy_ms(hx, hg, hs, hgx, dev, reps=2):
         t0 = time.perf_counter()
         for lo in range(0, n, chunk):
             m = min(chunk, n - lo)
-            with torch.cuda.stream(up):                         # contiguous rows, as the pipeline copies them
-                for t in range(T):
-                    stage_in[0, t, :m].copy_(hx[t, lo:lo + m], non_blocking=True)
-                    stage_in[1, t, :m].copy_(hg[t, lo:lo + m], non_blocking=True)
+            with torch.cuda.stream(up):
+                if pitched:
+                    _capi.copy_rows_(stage_in[0, :, :m], hx[:, lo:lo + m])
+                    _capi.copy_rows_(stage_in[1, :, :m], hg[:, lo:lo + m])
+                else:
+                    for t in range(T):
+                        stage_in[0, t, :m].copy_(hx[t, lo:lo + m], non_blocking=True)
+                        stage_in[1, t, :m].copy_(hg[t, lo:lo + m], non_blocking=True)
             with torch.cuda.stream(down):
-                for t in range(T):
-                    hs[t, lo:lo + m].copy_(stage_out[0, t, :m], non_blocking=True)
-                    hgx[t, lo:lo + m].copy_(stage_out[1, t, :m], non_blocking=True)
+                if pitched:
+                    _capi.copy_rows_(hs[:, lo:lo + m], stage_out[0, :, :m])
+                    _capi.copy_rows_(hgx[:, lo:lo + m], stage_out[1, :, :m])
+                else:
+                    for t in range(T):
+                        hs[t, lo:lo + m].copy_(stage_out[0, t, :m], non_blocking=True)
+                        hgx[t, lo:lo + m].copy_(stage_out[1, t, :m], non_blocking=True)
         torch.cuda.synchronize(dev)
         best = min(best, (time.perf_counter() - t0) * 1e3)
     return best
+
+
+def run_host_link(args):
+    """What limits the end-to-end (host-buffer) number when several ranks share one host: the same
+    host<->device traffic as the e2e leg (2^24 neurons per rank, T=8, fp32: 1 GiB each way per step),
+    copies only and with the kernels, under four variants of how the host side is driven. Every
+    figure is the max over ranks; GB/s is per rank and direction."""
+    import torch
+    import torch.distributed as dist
+    from snn_gpu_training_bptt_b200.host_pipeline import HostLifPipeline
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    T, n = T_STEPS, 1 << 24
+    cpus = sorted(os.sched_getaffinity(0))
+    per = max(1, len(cpus) // max(world, 1))
+    rows = []
+    for name, pitched, chunk, pin_cpu in (("T row copies per slab, chunk 2^22", False, 1 << 22, False),
+                                          ("one pitched copy per slab, chunk 2^22", True, 1 << 22, False),
+                                          ("one pitched copy per slab, chunk 2^24", True, 1 << 24, False),
+                                          ("pitched, chunk 2^22, rank bound to its own CPU cores before the "
+                                           "pinned buffers are allocated and touched", True, 1 << 22, True)):
+        if pin_cpu:
+            os.sched_setaffinity(0, cpus[rank * per:(rank + 1) * per] or cpus)
+        bufs = [torch.empty((T, n), dtype=torch.float32).pin_memory() for _ in range(4)]
+        for b in bufs:
+            b.zero_()
+        bufs[0].normal_(0.5, 1.0)
+        bufs[1].normal_(0.0, 1.0)
+        if world > 1:
+            dist.barrier()
+        copy_ms = _host_link_copy_ms(*bufs, dev, reps=2, chunk=chunk, pitched=pitched)
+        pipe = HostLifPipeline(T, n, torch.float32, chunk=chunk, lanes=3, device=dev, pitched=pitched)
+        pipe.run(*bufs, ALPHA, THRESH, BETA, INTERVAL)
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize(dev)
+        t0 = time.perf_counter()
+        for _ in range(3):
+            pipe.run(*bufs, ALPHA, THRESH, BETA, INTERVAL)
+        torch.cuda.synchronize(dev)
+        e2e_ms = (time.perf_counter() - t0) / 3 * 1e3
+        if world > 1:
+            t = torch.tensor([copy_ms, e2e_ms], device=dev, dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            copy_ms, e2e_ms = float(t[0]), float(t[1])
+        nbytes = 2 * T * n * 4
+        rows.append({"variant": name, "copy_only_ms": round(copy_ms, 2), "copy_gbs_each_way_per_rank": round(nbytes / copy_ms / 1e6, 2),
+                     "e2e_ms": round(e2e_ms, 2), "e2e_gbs_aggregate": round(gbps(n * world, e2e_ms / 1e3), 2)})
+        del bufs, pipe
+        if pin_cpu:
+            os.sched_setaffinity(0, cpus)
+    if rank == 0:
+        print(json.dumps({"metric": "host_link_gbs", "n_gpus": world, "cpus_visible": len(cpus),
+                          "config": {"workload": "host<->device traffic of the e2e leg, T=8, 2^24 neurons per rank, fp32"},
+                          "rows": rows}))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
 
 
 def _time_graphed(fn, reps=20, per_graph=10):
@@ -769,11 +843,12 @@ def main():
                     help="--workload linear_lif only: run this many plain forward+backward steps and exit (for profiler captures)")
     ap.add_argument("--no-trainer", action="store_true", help="skip the spiking-CNN training legs")
     ap.add_argument("--no-resnet", action="store_true", help="skip the ResNet-19-style training leg")
+    ap.add_argument("--bucket-mb", type=float, default=25.0, help="gradient bucket size of the training legs (MB)")
     ap.add_argument("--no-linear-lif", action="store_true", help="skip the fused linear + LIF (tensor-core) leg")
     ap.add_argument("--trainer-steps", type=int, default=30)
     ap.add_argument("--log2n", type=int, default=26,
                     help="log2 of neurons per GPU (26 = the benchmark size; smaller only for profiler captures)")
-    ap.add_argument("--workload", default="lif", choices=["lif", "sweep", "bn_lif", "linear_lif"],
+    ap.add_argument("--workload", default="lif", choices=["lif", "sweep", "bn_lif", "linear_lif", "host_link"],
                     help="lif = the benchmark line; the others are secondary single-GPU measurements")
     args = ap.parse_args()
     if args.impl == "reference":
@@ -784,6 +859,8 @@ def main():
         run_bn_lif(args)
     elif args.workload == "linear_lif":
         run_linear_lif(args)
+    elif args.workload == "host_link":
+        run_host_link(args)
     else:
         run_ours(args)
 

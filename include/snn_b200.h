@@ -112,6 +112,17 @@ int snn_lif_bwd(const void *x, const void *grad_spike, void *grad_x, int64_t T, 
 int snn_spike_unpack(const void *bits, void *spike, int64_t T, int64_t N, int dtype,
                      void *stream);
 
+/*
+ * Copy `rows` rows of `row_bytes` bytes between (pinned) host memory and device memory in one
+ * pitched transfer: row r goes from src + r*src_pitch to dst + r*dst_pitch. to_device != 0 =
+ * host -> device, 0 = device -> host. One call moves a [T, chunk] slab of a time-major [T, N]
+ * host tensor (pitch N*element size) to or from a dense staging buffer: it is what the
+ * host-buffer pipeline uses instead of T separate row copies. No counterpart in the reference
+ * (its tensors are created on the device).
+ */
+int snn_copy_rows_async(void *dst, size_t dst_pitch, const void *src, size_t src_pitch,
+                        size_t row_bytes, int64_t rows, int to_device, void *stream);
+
 /* ----------------------------------------------------------------------------------------
  * Batch-norm family. Tensors are [T, N] time-major with N = B * C * inner; the channel of flat
  * neuron index n is (n / inner) % C: inner = H*W for contiguous [T,B,C,H,W], inner = 1 for

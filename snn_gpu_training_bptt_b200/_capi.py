@@ -27,6 +27,7 @@ SIGNATURES = {
     "snn_lif_bwd_workspace_bytes": (_i64, [_i64, _i64, _int]),
     "snn_lif_bwd": (_int, [_vp, _vp, _vp, _i64, _i64, _int, _f32, _f32, _f32, _f32, _vp, _sz, _vp]),
     "snn_spike_unpack": (_int, [_vp, _vp, _i64, _i64, _int, _vp]),
+    "snn_copy_rows_async": (_int, [_vp, _sz, _vp, _sz, _sz, _i64, _int, _vp]),
     "snn_lif_bwd_noalloc": (_int, [_vp, _vp, _vp, _i64, _i64, _int, _f32, _f32, _f32, _f32, _vp]),
     "snn_lif_pool_fwd": (_int, [_vp, _vp, _i64, _i64, _i64, _i64, _i64, _int, _f32, _f32, _vp]),
     "snn_lif_pool_bwd": (_int, [_vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _int, _f32, _f32, _f32, _f32, _vp]),
@@ -191,6 +192,26 @@ def lif_bwd(x, grad_spike, alpha, thresh, beta, interval):
                                float(beta), float(interval), _ptr(ws), need, _stream(x.device))
     check("snn_lif_bwd", rc)
     return gx
+
+
+def copy_rows_(dst, src):
+    """One pitched transfer between a host and a device 2-D tensor view (rows may be strided, the
+    elements of a row must be contiguous): dst[r, :] = src[r, :] on torch's current stream."""
+    if dst.dim() != 2 or src.dim() != 2 or dst.shape != src.shape or dst.dtype != src.dtype:
+        raise ValueError("copy_rows_: dst and src must be 2-D views of the same shape and dtype")
+    if dst.is_cuda == src.is_cuda:
+        raise ValueError("copy_rows_: one side must be host memory, the other device memory")
+    rows, cols = dst.shape
+    if rows and cols and (dst.stride(1) != 1 or src.stride(1) != 1):
+        raise ValueError("copy_rows_: rows must be contiguous")
+    es = dst.element_size()
+    dev = dst.device if dst.is_cuda else src.device
+    with torch.cuda.device(dev):
+        rc = lib().snn_copy_rows_async(_ptr(dst), dst.stride(0) * es if rows > 1 else cols * es, _ptr(src),
+                                       src.stride(0) * es if rows > 1 else cols * es, cols * es, rows,
+                                       1 if dst.is_cuda else 0, _stream(dev))
+    check("snn_copy_rows_async", rc)
+    return dst
 
 
 def spike_unpack(bits, T, dtype=torch.float32):

@@ -332,4 +332,17 @@ int snn_spike_unpack(const void* bits, void* spike, int64_t T, int64_t N, int dt
     return check_launch();
 }
 
+int snn_copy_rows_async(void* dst, size_t dst_pitch, const void* src, size_t src_pitch, size_t row_bytes,
+                        int64_t rows, int to_device, void* stream) {
+    if (rows < 0) return SNN_ERR_SHAPE;
+    if (rows == 0 || row_bytes == 0) return SNN_OK;
+    if (!dst || !src) return SNN_ERR_NULL;
+    if (dst_pitch < row_bytes || src_pitch < row_bytes) return SNN_ERR_SHAPE;
+    cudaError_t e = cudaMemcpy2DAsync(dst, dst_pitch, src, src_pitch, row_bytes, static_cast<size_t>(rows),
+                                      to_device ? cudaMemcpyHostToDevice : cudaMemcpyDeviceToHost,
+                                      static_cast<cudaStream_t>(stream));
+    if (e != cudaSuccess) { snn_internal::set_last_cuda_error(static_cast<int>(e)); return SNN_ERR_CUDA; }
+    return SNN_OK;
+}
+
 }  // extern "C"

@@ -177,6 +177,60 @@ def run(model_name="vgg", time_steps=8, batch=64, steps=20, warmup=5, precision=
     return out
 
 
+def bucket_timeline(model_name="vgg", time_steps=8, batch=64, precision="bf16", bucket_mb=25.0, steps=3):
+    """Per-bucket timing of the overlapped all-reduce over a few EAGER steps (CUDA events cannot be
+    timed inside a captured graph): for every bucket, milliseconds from the start of the step to the
+    moment its last gradient exists (ready), to the start and to the end of its all-reduce on the
+    side stream, and the time at which backward itself ends. Medians over ``steps`` steps."""
+    import statistics
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    own_group = False
+    if world > 1 and not dist.is_initialized():
+        dist.init_process_group("nccl", device_id=dev)
+        own_group = True
+    act_dtype = {"bf16": torch.bfloat16, "fp16": torch.float16, "fp32": torch.float32}[precision]
+    torch.backends.cudnn.benchmark = True
+    torch.manual_seed(0)
+    net = models.build(model_name, time_steps=time_steps, act_dtype=act_dtype).to(dev)
+    model = DistributedDataParallel(net, bucket_mb=bucket_mb)
+    opt = torch.optim.SGD(net.parameters(), lr=1e-2, momentum=0.9)
+    images = torch.rand(batch, 3, 32, 32, device=dev)
+    labels = torch.randint(0, 10, (batch,), device=dev)
+    rows = []
+    for k in range(5 + steps):
+        model.trace = [] if k >= 5 else None
+        torch.cuda.synchronize(dev)
+        if world > 1:
+            dist.barrier()
+        e0, e1, e2 = (torch.cuda.Event(enable_timing=True) for _ in range(3))
+        e0.record()
+        model.zero_grad()
+        loss = F.cross_entropy(model(images), labels)
+        e1.record()
+        loss.backward()
+        e2.record()
+        opt.step()
+        torch.cuda.synchronize(dev)
+        if model.trace is not None:
+            rows.append({"forward_end": e0.elapsed_time(e1), "backward_end": e0.elapsed_time(e2),
+                         "buckets": [(b, e0.elapsed_time(ev[0]), e0.elapsed_time(ev[1]), e0.elapsed_time(ev[2]))
+                                     for b, ev in model.trace]})
+    med = lambda vals: round(statistics.median(vals), 3)
+    out = {"model": model_name, "n_gpus": world, "bucket_mb": bucket_mb, "eager": True,
+           "bucket_bytes": [b["flat"].numel() * b["flat"].element_size() for b in model.buckets],
+           "forward_end_ms": med([r["forward_end"] for r in rows]), "backward_end_ms": med([r["backward_end"] for r in rows]),
+           "buckets": [{"bucket": i, "ready_ms": med([r["buckets"][i][1] for r in rows]),
+                        "allreduce_start_ms": med([r["buckets"][i][2] for r in rows]),
+                        "allreduce_end_ms": med([r["buckets"][i][3] for r in rows])}
+                       for i in range(len(rows[0]["buckets"]))] if rows and rows[0]["buckets"] else []}
+    if own_group:
+        dist.destroy_process_group()
+    return out
+
+
 def profile_steps(model_name, time_steps, batch, precision, steps=3):
     """Kernel-level table (torch.profiler) of a few eager training steps on one GPU."""
     from torch.profiler import ProfilerActivity, profile
@@ -215,6 +269,8 @@ def main():
     ap.add_argument("--no-graph", action="store_true", help="issue every launch from Python instead of replaying a CUDA graph")
     ap.add_argument("--checkpoint", default=None)
     ap.add_argument("--log", action="store_true")
+    ap.add_argument("--bucket-timeline", action="store_true",
+                    help="print per-bucket ready / all-reduce start / end times of a few eager steps instead of timing")
     ap.add_argument("--profile", action="store_true",
                     help="print a torch.profiler kernel table of 3 eager single-GPU steps instead of timing")
     a = ap.parse_args()
@@ -226,6 +282,11 @@ def main():
     B = a.batch or (64 if a.model == "vgg" else 128)
     if a.profile:
         print(profile_steps(a.model, T, B, a.precision))
+        return
+    if a.bucket_timeline:
+        res = bucket_timeline(a.model, T, B, a.precision, a.bucket_mb)
+        if int(os.environ.get("RANK", "0")) == 0:
+            print(json.dumps(res))
         return
     res = run(a.model, T, B, a.steps, a.warmup, a.precision, bucket_mb=a.bucket_mb,
               overlap=not a.no_overlap, log=a.log, checkpoint=a.checkpoint, graph=not a.no_graph)

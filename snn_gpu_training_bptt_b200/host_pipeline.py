@@ -19,10 +19,11 @@ class HostLifPipeline:
     ``lanes`` concurrent streams (each owns one set of device staging buffers).
     """
 
-    def __init__(self, T, N, dtype=torch.float32, chunk=1 << 22, lanes=3, device=None):
+    def __init__(self, T, N, dtype=torch.float32, chunk=1 << 22, lanes=3, device=None, pitched=True):
         if T > 32:
             raise ValueError("the host pipeline covers T <= 32 (longer time axes need a scratch tensor)")
         self.T, self.N, self.dtype = T, N, dtype
+        self.pitched = pitched          # one pitched copy per [T, chunk] slab instead of T row copies
         self.device = torch.device("cuda", torch.cuda.current_device()) if device is None else device
         self.chunk = min(chunk, N)
         self.lanes = []
@@ -50,9 +51,13 @@ class HostLifPipeline:
                     xv, gv, sv, gxv = xd, gd, sd, gxd
                 else:  # ragged last chunk: dense [T, n] views at the front of the buffers
                     xv, gv, sv, gxv = (b.view(-1)[:T * n].view(T, n) for b in (xd, gd, sd, gxd))
-                for t in range(T):
-                    xv[t].copy_(x_host[t, lo:lo + n], non_blocking=True)
-                    gv[t].copy_(g_host[t, lo:lo + n], non_blocking=True)
+                if self.pitched:
+                    _capi.copy_rows_(xv, x_host[:, lo:lo + n])
+                    _capi.copy_rows_(gv, g_host[:, lo:lo + n])
+                else:
+                    for t in range(T):
+                        xv[t].copy_(x_host[t, lo:lo + n], non_blocking=True)
+                        gv[t].copy_(g_host[t, lo:lo + n], non_blocking=True)
                 sp = _capi._stream(self.device)
                 _capi.check("snn_lif_fwd", lib.snn_lif_fwd(
                     _capi._ptr(xv), _capi._ptr(sv), None, None, T, n, code, float(alpha),
@@ -60,9 +65,13 @@ class HostLifPipeline:
                 _capi.check("snn_lif_bwd", lib.snn_lif_bwd(
                     _capi._ptr(xv), _capi._ptr(gv), _capi._ptr(gxv), T, n, code, float(alpha),
                     float(thresh), float(beta), float(interval), None, 0, sp))
-                for t in range(T):
-                    spike_host[t, lo:lo + n].copy_(sv[t], non_blocking=True)
-                    gx_host[t, lo:lo + n].copy_(gxv[t], non_blocking=True)
+                if self.pitched:
+                    _capi.copy_rows_(spike_host[:, lo:lo + n], sv)
+                    _capi.copy_rows_(gx_host[:, lo:lo + n], gxv)
+                else:
+                    for t in range(T):
+                        spike_host[t, lo:lo + n].copy_(sv[t], non_blocking=True)
+                        gx_host[t, lo:lo + n].copy_(gxv[t], non_blocking=True)
         for lane_stream, _ in self.lanes:
             caller.wait_stream(lane_stream)
         caller.synchronize()

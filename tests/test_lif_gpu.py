@@ -325,3 +325,22 @@ def test_full_size_T8_N64M_properties(capi):
     # power of two scales grad_x exactly
     gx2 = capi.lif_bwd(x, g * 2.0, A, TH, BE, IV)
     assert torch.equal(gx2, gx * 2.0)
+
+
+@pytest.mark.parametrize("pitched", [True, False])
+def test_host_buffer_pipeline_matches_the_oracle(capi, pitched):
+    """HostLifPipeline (pinned host tensors in, pinned host tensors out; chunks of the neuron axis on
+    several streams; one pitched copy per slab or T row copies) gives the oracle's spikes and
+    gradients, including a ragged last chunk."""
+    from snn_gpu_training_bptt_b200.host_pipeline import HostLifPipeline
+    T, N = 8, 3 * 4096 + 1234
+    x, g = seeded_inputs(T, N, seed=31)
+    hx, hg = x.view(T, N).contiguous().pin_memory(), g.view(T, N).contiguous().pin_memory()
+    hs, hgx = torch.empty((T, N)).pin_memory(), torch.empty((T, N)).pin_memory()
+    pipe = HostLifPipeline(T, N, torch.float32, chunk=4096, lanes=3, pitched=pitched)
+    for _ in range(2):                                   # the second run reuses the staging buffers
+        hs.fill_(float("nan")), hgx.fill_(float("nan"))
+        pipe.run(hx, hg, hs, hgx, **CONSTS)
+    s_ref, _ = orc.c_lif_fwd(hx.numpy())
+    assert np.array_equal(hs.numpy(), s_ref)
+    assert (hgx.numpy() == orc.c_lif_bwd(hx.numpy(), hg.numpy())).all()
