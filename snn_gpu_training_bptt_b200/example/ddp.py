@@ -23,7 +23,10 @@ This wrapper keeps the numerics and does overlap:
     apex's fallback has the same property: it always reduces the whole flat gradient set
     (distributed.py:491-510). Ranks that issued different numbers of all-reduces would hang NCCL;
   * ``finish()`` (called automatically at the end of backward through an autograd engine
-    callback) also makes the compute stream wait for the outstanding reductions.
+    callback) also makes the compute stream wait for the outstanding reductions - or, with
+    ``defer_wait=True``, leaves that to whoever consumes the gradients: ``wait_bucket(k)`` makes
+    the compute stream wait for bucket k only, so ``BucketSGD`` below updates the parameters of
+    the early buckets while the last (unhidable) all-reduce is still in flight.
 On CPU tensors (gloo) the same logic runs without streams.
 """
 import torch
@@ -31,13 +34,15 @@ import torch.distributed as dist
 
 
 class DistributedDataParallel(torch.nn.Module):
-    def __init__(self, module, bucket_mb=25.0, process_group=None, overlap=True, communicate=True, tail_mb=1.0):
+    def __init__(self, module, bucket_mb=25.0, process_group=None, overlap=True, communicate=True, tail_mb=1.0,
+                 defer_wait=False):
         """``communicate=False`` keeps all the bookkeeping but issues no all-reduce (a measuring aid:
         the step-time difference against the normal wrapper is the communication time that backward
         does not hide; gradients are then NOT averaged)."""
         super().__init__()
         self.module = module
         self.communicate = communicate
+        self.defer_wait = defer_wait
         self.trace = None           # set to [] to record (bucket, ready, start, end) CUDA events per reduction
         self.group = process_group
         self.world_size = dist.get_world_size(process_group) if dist.is_initialized() else 1
@@ -107,7 +112,8 @@ class DistributedDataParallel(torch.nn.Module):
                 p.grad = flat[offset:offset + p.numel()].view_as(p)
                 offset += p.numel()
                 self._bucket_of[p] = k
-            self.buckets.append({"flat": flat, "params": plist, "ready": 0})
+            done = torch.cuda.Event() if flat.is_cuda else None     # recorded after the bucket's all-reduce
+            self.buckets.append({"flat": flat, "params": plist, "ready": 0, "done": done})
 
     # ---- per-step ----------------------------------------------------------------------------
     def forward(self, *args, **kwargs):
@@ -173,6 +179,7 @@ class DistributedDataParallel(torch.nn.Module):
                 if events is not None:
                     events[2].record(self._comm_stream)
                     self.trace.append((k, events))
+                self.buckets[k]["done"].record(self._comm_stream)
             self._pending.append(k)
         else:
             self._all_reduce_mean(flat)
@@ -196,10 +203,55 @@ class DistributedDataParallel(torch.nn.Module):
         for b in self.buckets:
             b["ready"] = 0
         self._next_bucket = 0
-        if self._pending:
+        if self._pending and not self.defer_wait:
             flat = self.buckets[self._pending[0]]["flat"]
             torch.cuda.current_stream(flat.device).wait_stream(self._comm_stream)
             self._pending.clear()
 
+    def wait_bucket(self, k):
+        """Make the current stream wait for bucket k's all-reduce of this backward (a no-op when
+        that reduction ran inline). Only needed with ``defer_wait=True``."""
+        if k in self._pending:
+            torch.cuda.current_stream(self.buckets[k]["flat"].device).wait_event(self.buckets[k]["done"])
+            self._pending.remove(k)
+
     def bucket_sizes(self):
         return [b["flat"].numel() for b in self.buckets]
+
+
+class BucketSGD:
+    """``torch.optim.SGD`` with momentum that does not wait for the LAST all-reduce before it starts:
+    the parameters of all buckets but the last are updated first (after waiting for their reductions
+    only), then the last bucket's - the first layers, whose all-reduce cannot start before backward
+    ends and so cannot hide behind backward; it hides behind the first update instead. Two
+    ``torch.optim.SGD`` instances do the arithmetic, so the trajectory is that of the reference's
+    ``optim.SGD(..., momentum=0.9)`` (snnlib/example/train_test_cifar.py:36). Build the wrapper
+    with ``defer_wait=True``."""
+
+    def __init__(self, ddp, lr=1e-2, momentum=0.9):
+        self.ddp = ddp
+        n = len(ddp.buckets)
+        cut = n - 1 if n > 1 else n
+        self.groups = []                 # (index of the last bucket to wait for, optimizer of those buckets)
+        for lo, hi in ((0, cut), (cut, n)):
+            params = [p for b in ddp.buckets[lo:hi] for p in b["params"]]
+            if params:
+                self.groups.append((hi - 1, torch.optim.SGD(params, lr=lr, momentum=momentum)))
+
+    def zero_grad(self, set_to_none=False):
+        self.ddp.zero_grad()
+
+    def step(self):
+        done = 0
+        for last, opt in self.groups:
+            for k in range(done, last + 1):
+                self.ddp.wait_bucket(k)
+            done = last + 1
+            opt.step()
+
+    def state_dict(self):
+        return {"groups": [opt.state_dict() for _, opt in self.groups]}
+
+    def load_state_dict(self, state):
+        for (_, opt), saved in zip(self.groups, state["groups"]):
+            opt.load_state_dict(saved)

@@ -23,7 +23,7 @@ import torch.distributed as dist
 import torch.nn.functional as F
 
 from . import models
-from .ddp import DistributedDataParallel
+from .ddp import BucketSGD, DistributedDataParallel
 
 
 class SyntheticImages:
@@ -62,13 +62,17 @@ def load_checkpoint(path, model, optimizer=None):
 
 def run(model_name="vgg", time_steps=8, batch=64, steps=20, warmup=5, precision="bf16", lr=1e-2,
         bucket_mb=25.0, overlap=True, seed=0, log=False, checkpoint=None, graph=True,
-        return_params=False, model_kwargs=None, communicate=True):
+        return_params=False, model_kwargs=None, communicate=True, bucket_sgd=False, prefetch_input=True):
     """Trains for warmup+steps steps; returns a dict with samples/sec (whole job) and timings.
 
     ``graph=True`` captures one whole training step (zero_grad, forward, loss, backward with its
     bucketed all-reduces on the side stream, SGD update) into a CUDA graph after the warm-up steps
     and replays it: a step is ~150 small launches, and at a few ms per step the Python/launch
-    overhead of issuing them one by one is as large as the GPU time itself."""
+    overhead of issuing them one by one is as large as the GPU time itself.
+
+    ``bucket_sgd=True`` swaps ``torch.optim.SGD`` for ``ddp.BucketSGD`` (the update of the early
+    buckets overlaps the last all-reduce). Measured on the VGG-style network it does not pay: the
+    second, small optimizer step costs ~40 us of launches, about what the overlap saves at 8 GPUs."""
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
@@ -83,19 +87,54 @@ def run(model_name="vgg", time_steps=8, batch=64, steps=20, warmup=5, precision=
     torch.backends.cudnn.benchmark = True
     torch.manual_seed(seed)
     net = models.build(model_name, time_steps=time_steps, act_dtype=act_dtype, **(model_kwargs or {})).to(dev)
-    model = DistributedDataParallel(net, bucket_mb=bucket_mb, overlap=overlap, communicate=communicate)
-    opt = torch.optim.SGD(net.parameters(), lr=lr, momentum=0.9)
+    model = DistributedDataParallel(net, bucket_mb=bucket_mb, overlap=overlap, communicate=communicate,
+                                    defer_wait=bucket_sgd)
+    if bucket_sgd:
+        opt = BucketSGD(model, lr=lr, momentum=0.9)     # updates bucket by bucket as the all-reduces land
+    else:
+        opt = torch.optim.SGD(net.parameters(), lr=lr, momentum=0.9)
     data = SyntheticImages(batch, seed=1000 + rank)
     n_params = sum(p.numel() for p in net.parameters())
 
     static_images = torch.empty((batch, 3, 32, 32), device=dev)
     static_labels = torch.empty((batch,), dtype=torch.long, device=dev)
+    # The next batch travels host -> device on its own stream while the current step computes (two
+    # staging buffers); the step then starts with a device-to-device copy into the fixed buffers the
+    # captured graph reads. With several ranks on one host link the upload is several times slower
+    # than alone (measured 12 GB/s per rank at 8 GPUs against 49 GB/s), which would otherwise sit in
+    # front of every step.
+    copy_stream = torch.cuda.Stream(dev)
+    staged = [(torch.empty_like(static_images), torch.empty_like(static_labels), torch.cuda.Event()) for _ in range(2)]
+    consumed = [torch.cuda.Event() for _ in range(2)]
+
+    def prefetch(k):
+        j, (img, lab, ready) = k % len(data.images), staged[k % 2]
+        copy_stream.wait_event(consumed[k % 2])          # the step that last read this staging buffer
+        with torch.cuda.stream(copy_stream):
+            img.copy_(data.images[j], non_blocking=True)
+            lab.copy_(data.labels[j], non_blocking=True)
+            ready.record(copy_stream)
+
+    state = {"prefetched": None}
 
     def load(k):
-        """This step's batch: pinned host memory -> the fixed device buffers the step reads."""
-        j = k % len(data.images)
-        static_images.copy_(data.images[j], non_blocking=True)
-        static_labels.copy_(data.labels[j], non_blocking=True)
+        """This step's batch: pinned host memory -> staging (prefetched during the step before) ->
+        the fixed device buffers the step reads; then the upload of step k+1's batch is started."""
+        if not prefetch_input:
+            j = k % len(data.images)
+            static_images.copy_(data.images[j], non_blocking=True)
+            static_labels.copy_(data.labels[j], non_blocking=True)
+            return
+        if state["prefetched"] != k:
+            prefetch(k)
+        img, lab, ready = staged[k % 2]
+        cur = torch.cuda.current_stream(dev)
+        cur.wait_event(ready)
+        static_images.copy_(img, non_blocking=True)
+        static_labels.copy_(lab, non_blocking=True)
+        consumed[k % 2].record(cur)
+        prefetch(k + 1)
+        state["prefetched"] = k + 1
 
     def compute():
         model.zero_grad()

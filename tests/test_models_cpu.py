@@ -115,3 +115,31 @@ def test_reference_networks_keep_their_state_dict_layout():
     for name, want in layouts.items():
         sd = getattr(models, name)().state_dict()
         assert {k: list(v.shape) for k, v in sd.items()} == want, name
+
+
+def test_bucket_sgd_follows_torch_sgd_and_round_trips_its_state():
+    """BucketSGD (per-bucket momentum SGD used by the trainer) against torch.optim.SGD on the same
+    gradients, and its state dict through save / load."""
+    from snn_gpu_training_bptt_b200.example.ddp import BucketSGD, DistributedDataParallel as DDP
+    torch.manual_seed(3)
+    make = lambda: torch.nn.Sequential(torch.nn.Linear(6, 16), torch.nn.Tanh(), torch.nn.Linear(16, 16), torch.nn.Tanh(),
+                                       torch.nn.Linear(16, 3))
+    a, b = make(), make()
+    b.load_state_dict(a.state_dict())
+    ddp = DDP(a, bucket_mb=0.0005, defer_wait=True)
+    assert len(ddp.buckets) > 2
+    mine, ref = BucketSGD(ddp, lr=0.05, momentum=0.9), torch.optim.SGD(b.parameters(), lr=0.05, momentum=0.9)
+    x, y = torch.randn(4, 5, 6), torch.randn(4, 5, 3)
+    for step in range(4):
+        mine.zero_grad(), ref.zero_grad()
+        (a(x[step]) - y[step]).square().mean().backward()
+        (b(x[step]) - y[step]).square().mean().backward()
+        mine.step(), ref.step()
+        if step == 1:
+            saved = mine.state_dict()
+            restored = BucketSGD(ddp, lr=0.0, momentum=0.0)
+            restored.load_state_dict(saved)
+            assert restored.groups[0][1].param_groups[0]["lr"] == 0.05
+            mine = restored
+    for p, q in zip(a.parameters(), b.parameters()):
+        assert torch.allclose(p, q, rtol=1e-6, atol=1e-7)
