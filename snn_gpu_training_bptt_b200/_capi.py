@@ -52,6 +52,31 @@ SIGNATURES = {
 STATIC_SCRATCH_BYTES = 64 * 1024 * 1024
 
 
+# NVTX ranges around every op (and, in example/ddp.py, around every gradient bucket's all-reduce), so
+# that a timeline tool shows which layer's kernels and which bucket a span belongs to. Off unless
+# SNN_NVTX=1: a range push/pop per op is host work the hot loop does not need. The reference's DDP
+# has the same hooks behind its `prof` switch (apex/parallel/distributed.py:359-360, 516-517).
+NVTX = os.environ.get("SNN_NVTX", "0") == "1"
+
+
+def nvtx_range(name):
+    """Decorator: run the function inside an NVTX range called ``name`` when SNN_NVTX=1."""
+    def wrap(fn):
+        if not NVTX:
+            return fn
+        import functools
+
+        @functools.wraps(fn)
+        def inner(*args, **kwargs):
+            torch.cuda.nvtx.range_push(name)
+            try:
+                return fn(*args, **kwargs)
+            finally:
+                torch.cuda.nvtx.range_pop()
+        return inner
+    return wrap
+
+
 class SnnError(RuntimeError):
     """A C-ABI call returned a non-zero snn_status."""
 
@@ -148,6 +173,7 @@ def bits_dtype(T):
     return torch.uint8 if T <= 8 else (torch.int16 if T <= 16 else torch.int32)
 
 
+@nvtx_range("snn.lif_fwd")
 def lif_fwd(x, alpha, thresh, want_spike=True, want_mem=False, want_bits=False):
     """Run snn_lif_fwd on a [T, ...] CUDA tensor; returns (spike, mem, bits) with None for
     outputs not requested. Launches on torch's current stream of x's device."""
@@ -167,6 +193,7 @@ def lif_fwd(x, alpha, thresh, want_spike=True, want_mem=False, want_bits=False):
     return spike, mem, bits
 
 
+@nvtx_range("snn.lif_bwd")
 def lif_bwd(x, grad_spike, alpha, thresh, beta, interval):
     """Run snn_lif_bwd; returns grad_x shaped like x."""
     _require_cuda(x, "spatial")
@@ -280,6 +307,7 @@ def _f32c(t, C, name):
     return t.contiguous()
 
 
+@nvtx_range("snn.bn_lif_fwd")
 def bn_lif_fwd(x, weight, bias, var, mean, eps, alpha, thresh, fire=True, want_mem=False, ivar=None):
     """snn_bn_lif_fwd. Returns (ivar, out, mem): out = spikes (fire) or the normalised tensor.
     Pass ``var=None, ivar=<tensor>`` to rebuild with w' = weight*ivar (backward-time form)."""
@@ -302,6 +330,7 @@ def bn_lif_fwd(x, weight, bias, var, mean, eps, alpha, thresh, fire=True, want_m
     return ivar, out, mem
 
 
+@nvtx_range("snn.bn_lif_bwd_sums")
 def bn_lif_bwd_sums(x, grad, weight, bias, ivar, mean, alpha, thresh, beta, interval, fire=True):
     """snn_bn_lif_bwd_sums. Returns (x_dense, grad_dense, sum_g, sum_gx, count) where count is the
     number of values per channel (T*B*inner)."""
@@ -330,6 +359,7 @@ def bn_channel_means(sum_g, sum_gx, weight, count):
     return out[0], out[1]
 
 
+@nvtx_range("snn.bn_lif_bwd_input")
 def bn_lif_bwd_input(x, grad, weight, bias, ivar, mean, gxhat, gxhatx, alpha, thresh, beta, interval,
                      fire=True):
     """snn_bn_lif_bwd_input. Returns grad_x laid out like x."""
@@ -365,6 +395,7 @@ def _channels_last_5d(x):
     return out
 
 
+@nvtx_range("snn.lif_pool_fwd")
 def lif_pool_fwd(x, alpha, thresh):
     """Pooled spikes [T, B, C, H/2, W/2] (channels-last memory order) of the LIF of x."""
     _require_cuda(x, "spatial")
@@ -382,6 +413,7 @@ def lif_pool_fwd(x, alpha, thresh):
     return x, out
 
 
+@nvtx_range("snn.lif_pool_bwd")
 def lif_pool_bwd(x, grad_out, alpha, thresh, beta, interval):
     """grad w.r.t. x (channels-last, as produced by lif_pool_fwd's first return value)."""
     T, B, C, H, W = x.shape
@@ -410,6 +442,7 @@ def _channel_geometry(t):
     return None
 
 
+@nvtx_range("snn.channel_bias_add")
 def channel_bias_add_(y, bias):
     """y[:, c] += bias[c] in place (y: [N, C, ...] contiguous or channels-last; bias fp32 [C])."""
     geo = _channel_geometry(y)
@@ -423,6 +456,7 @@ def channel_bias_add_(y, bias):
     return y
 
 
+@nvtx_range("snn.channel_sum")
 def channel_sum(grad):
     """fp32 [C] sums of grad ([N, C, ...]) over every axis but the channel axis."""
     geo = _channel_geometry(grad)
@@ -449,6 +483,7 @@ def linear_lif_supported(x, weight):
     return bool(lib().snn_linear_lif_fwd_supported(T, B, K, weight.shape[0], DTYPE_CODE[x.dtype]))
 
 
+@nvtx_range("snn.linear_lif_fwd")
 def linear_lif_fwd(x, weight, bias, alpha, thresh, want_current=True):
     """(current, spike) of ``LIF(x @ weight^T + bias)`` in one kernel. x [T, B, K] bf16, weight
     [M, K] (cast to bf16 if needed), bias fp32 [M] or None."""
@@ -479,6 +514,7 @@ def linear_lif_bwd_supported(x, weight):
     return bool(lib().snn_linear_lif_bwd_supported(T, B, K, weight.shape[0], DTYPE_CODE[x.dtype]))
 
 
+@nvtx_range("snn.linear_lif_bwd")
 def linear_lif_bwd(x, weight, current, grad_spike, alpha, thresh, beta, interval, need_grad_x=True,
                    need_grad_weight=True, need_grad_bias=True, grad_weight_dtype=torch.float32):
     """(grad_x, grad_weight, grad_bias) of ``LIF(x @ weight^T + bias)`` from the saved LIF input

@@ -29,8 +29,12 @@ This wrapper keeps the numerics and does overlap:
     the early buckets while the last (unhidable) all-reduce is still in flight.
 On CPU tensors (gloo) the same logic runs without streams.
 """
+import os
+
 import torch
 import torch.distributed as dist
+
+from .. import _capi
 
 
 class DistributedDataParallel(torch.nn.Module):
@@ -56,7 +60,9 @@ class DistributedDataParallel(torch.nn.Module):
         self._comm_stream = None
         dev = self.params[0].device if self.params else torch.device("cpu")
         if dev.type == "cuda":
-            self._comm_stream = torch.cuda.Stream(dev)
+            # SNN_DDP_COMM_PRIORITY=-1 runs the reductions on a high-priority stream
+            prio = int(os.environ.get("SNN_DDP_COMM_PRIORITY", "0"))
+            self._comm_stream = torch.cuda.Stream(dev, priority=prio)
         # NCCL averages in the reduction itself; gloo needs sum followed by a scale
         backend = dist.get_backend(process_group) if dist.is_initialized() else ""
         self._avg_op = dist.ReduceOp.AVG if backend == "nccl" else None
@@ -185,6 +191,16 @@ class DistributedDataParallel(torch.nn.Module):
             self._all_reduce_mean(flat)
 
     def _all_reduce_mean(self, flat):
+        if _capi.NVTX and flat.is_cuda:
+            torch.cuda.nvtx.range_push("snn.ddp.allreduce %d bytes" % (flat.numel() * flat.element_size()))
+            try:
+                self._all_reduce_mean_impl(flat)
+            finally:
+                torch.cuda.nvtx.range_pop()
+        else:
+            self._all_reduce_mean_impl(flat)
+
+    def _all_reduce_mean_impl(self, flat):
         if self._avg_op is not None:
             dist.all_reduce(flat, op=self._avg_op, group=self.group)
         else:

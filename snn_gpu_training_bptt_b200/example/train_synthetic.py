@@ -61,7 +61,7 @@ def load_checkpoint(path, model, optimizer=None):
 
 
 def run(model_name="vgg", time_steps=8, batch=64, steps=20, warmup=5, precision="bf16", lr=1e-2,
-        bucket_mb=25.0, overlap=True, seed=0, log=False, checkpoint=None, graph=True,
+        bucket_mb=64.0, overlap=True, seed=0, log=False, checkpoint=None, graph=True,
         return_params=False, model_kwargs=None, communicate=True, bucket_sgd=False, prefetch_input=True):
     """Trains for warmup+steps steps; returns a dict with samples/sec (whole job) and timings.
 
@@ -303,7 +303,7 @@ def main():
     ap.add_argument("--steps", type=int, default=30)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--precision", default="bf16", choices=["bf16", "fp16", "fp32"])
-    ap.add_argument("--bucket-mb", type=float, default=25.0)
+    ap.add_argument("--bucket-mb", type=float, default=64.0)
     ap.add_argument("--no-overlap", action="store_true")
     ap.add_argument("--no-graph", action="store_true", help="issue every launch from Python instead of replaying a CUDA graph")
     ap.add_argument("--checkpoint", default=None)
