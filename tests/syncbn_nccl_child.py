@@ -52,6 +52,13 @@ def main():
         return res
 
     res = run(build(True), slice(2 * rank, 2 * rank + 2))
+    # the same sync-BN layers on bf16 activations: statistics are all-reduced in fp32
+    conv16, fc16, _ = build(True)
+    xi = x[:, 2 * rank:2 * rank + 2].contiguous().to(torch.bfloat16).requires_grad_(True)
+    y16 = conv16(xi)
+    y16.backward(gy_conv[:, 2 * rank:2 * rank + 2].contiguous().to(torch.bfloat16))
+    res["bf16_y_conv"], res["bf16_gx_conv"] = y16.detach().float().cpu(), xi.grad.float().cpu()
+    res["bf16_running_var"] = conv16.running_var.detach().cpu()
     torch.save(res, os.path.join(out_dir, f"rank{rank}.pt"))
     if rank == 0:
         torch.save(run(build(False), slice(0, 4)), os.path.join(out_dir, "single.pt"))

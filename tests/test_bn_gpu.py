@@ -207,6 +207,35 @@ def test_fused_compositions_against_gold(capi, bn_golden, key):
     close(getattr(mod, wname).grad, g[key + "_glw"], what="gw_lin"); close(getattr(mod, bname).grad, g[key + "_glb"], what="gb_lin")
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_bn_modules_run_in_16_bit_with_fp32_statistics(capi, dtype):
+    """Bn, BnFire, BnFireFc and BnFireConv on 16-bit activations (the trainer's precision): the
+    statistics the modules compute are fp32 and equal an fp32 computation on the same values, the
+    outputs equal the C ABI fed those statistics, the running statistics stay fp32, and backward
+    produces finite gradients of the right types."""
+    from snn_gpu_training_bptt_b200 import snnlib_op as sop
+    gen = torch.Generator().manual_seed(17)
+    x5 = (torch.randn((6, 4, 8, 6, 6), generator=gen) * 1.2 + 0.1).to(dtype).cuda()
+    x3 = (torch.randn((6, 16, 8), generator=gen) * 1.2 + 0.1).to(dtype).cuda()
+    for mod, x in ((sop.BnFire(8, (0, 1, 3, 4)), x5), (sop.Bn(8, (0, 1)), x3), (sop.BnFire(8, (0, 1)), x3),
+                   (sop.BnFireConv(8, 16), x5), (sop.BnFireFc(8, 5, (0, 1)), x3)):
+        mod = mod.cuda()
+        var, mean = mod._statistics(x)
+        assert var.dtype == mean.dtype == torch.float32
+        v32, m32 = torch.var_mean(x.float(), dim=mod.dim_bn, unbiased=False)
+        close(mean, m32, 1e-5, "mean"); close(var, v32, 1e-4, "var")
+        xi = x.clone().requires_grad_(True)
+        y = mod(xi)
+        assert y.dtype == dtype and mod.running_var.dtype == torch.float32
+        y.backward(torch.randn(y.shape, device="cuda").to(dtype))
+        assert xi.grad.dtype == dtype and torch.isfinite(xi.grad.float()).all()
+        assert mod.weight_bn.grad.dtype == torch.float32 and torch.isfinite(mod.weight_bn.grad).all()
+        if isinstance(mod, sop.BnFire):
+            # spikes equal the kernel's own output for the same fp32 statistics
+            _, want, _ = capi.bn_lif_fwd(x, mod.weight_bn.detach(), mod.bias_bn.detach(), var, mean, mod.eps_bn, A, TH)
+            assert torch.equal(y.detach(), want)
+
+
 def test_bn_argument_errors(capi):
     x = torch.zeros(4, 2, 8, 3, 3, device="cuda")
     w = torch.ones(8, device="cuda")
@@ -237,6 +266,14 @@ def test_sync_bn_layers_over_nccl(tmp_path):
     assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-3000:]
     single = torch.load(str(tmp_path / "single.pt"))
     ranks = [torch.load(str(tmp_path / f"rank{r}.pt")) for r in range(2)]
+    # bf16 activations through the sync-BN conv layer: fp32 statistics identical on both ranks, output
+    # and input gradient near the fp32 run (bf16 rounding of activations and of the convolution)
+    assert ranks[0]["bf16_running_var"].dtype == torch.float32
+    assert torch.equal(ranks[0]["bf16_running_var"], ranks[1]["bf16_running_var"])
+    y16 = torch.cat([ranks[0]["bf16_y_conv"], ranks[1]["bf16_y_conv"]], dim=1)
+    assert torch.isfinite(y16).all()
+    rel = float((y16 - single["y_conv"]).norm() / single["y_conv"].norm())
+    assert rel < 0.2, rel
     for name in single:
         if name.startswith(("y_", "gx_")):
             both = torch.cat([ranks[0][name], ranks[1][name]], dim=1)
