@@ -673,7 +673,9 @@ def run_sweep(args):
 
 
 def run_bn_lif(args):
-    """BN-fused LIF forward + two-pass backward, fp32, [T=8, B=256, C=256, 32x32] (N = 2^26)."""
+    """BN-fused LIF forward + two-pass backward, fp32, T=8, N = 2^26: contiguous [B=256, C=256, 32x32]
+    images (channel runs of 1024 neurons) and the same tensor in channels-last memory order
+    (every neuron its own channel run: the layout of the trainer's images and of [T, B, C] inputs)."""
     import torch
     from snn_gpu_training_bptt_b200 import _capi
     peak, peak_src = measured_peak()
@@ -681,40 +683,47 @@ def run_bn_lif(args):
     torch.cuda.set_device(dev)
     T, B, C, HW = 8, 256 >> (26 - args.log2n), 256, 1024
     N = B * C * HW
-    gen = torch.Generator(device=dev).manual_seed(1234)
-    x = torch.randn((T, B, C, 32, 32), device=dev, generator=gen) * 1.5 + 0.3
-    g = torch.randn((T, B, C, 32, 32), device=dev, generator=gen)
-    w = torch.rand(C, device=dev, generator=gen) + 0.5
-    b = torch.randn(C, device=dev, generator=gen) * 0.2
-    var, mean = torch.var_mean(x, dim=(0, 1, 3, 4), unbiased=False)
-    L, sp = _capi.lib(), _capi._stream(dev)
-    out, gx = torch.empty_like(x), torch.empty_like(x)
-    ivar = torch.empty_like(w)
-    sums = torch.empty((2, C), device=dev)
-    means = torch.empty((2, C), device=dev)
-    P = _capi._ptr
-    fwd = lambda: L.snn_bn_lif_fwd(P(x), P(w), P(b), P(var), P(mean), 1e-5, P(out), None, P(ivar), T, N, C, HW, 0, 1,
-                                   ALPHA, THRESH, sp)
-    assert fwd() == 0
-    def bwd():
-        rc = L.snn_bn_lif_bwd_sums(P(x), P(g), P(w), P(b), P(ivar), P(mean), P(sums[0]), P(sums[1]), T, N, C, HW, 0, 1,
-                                   ALPHA, THRESH, BETA, INTERVAL, sp)
-        rc |= L.snn_bn_channel_means(P(sums[0]), P(sums[1]), P(w), P(means[0]), P(means[1]), C, float(T * N // C), sp)
-        rc |= L.snn_bn_lif_bwd_input(P(x), P(g), P(w), P(b), P(ivar), P(mean), P(means[0]), P(means[1]), P(gx), T, N, C,
-                                     HW, 0, 1, ALPHA, THRESH, BETA, INTERVAL, sp)
-        assert rc == 0
-    t_f = _time_kernel(fwd, args.steps if args.steps < 50 else 20)
-    t_b = _time_kernel(bwd, args.steps if args.steps < 50 else 20)
-    gb = lambda nbytes, ms: nbytes * T * N / ms / 1e6
-    print(json.dumps({
-        "metric": "bn_lif_fwd_bwd_hbm_gbps", "value": round(gb(28, t_f + t_b), 1), "unit": "GB/s", "dtype": "f32",
-        "config": {"workload": f"bn_fire fwd + 2-pass bwd fp32 T=8 [B={B},C=256,32x32] N=2^{args.log2n}",
-                   "bytes_per_neuron_step": "fwd 8, bwd sums pass 8 + input pass 12",
-                   "l2": "working set > L2"},
-        "fwd_ms": round(t_f, 4), "fwd_gbs": round(gb(8, t_f), 1), "bwd_ms": round(t_b, 4),
-        "bwd_gbs": round(gb(20, t_b), 1), "frac_of_peak": round(gb(28, t_f + t_b) / peak, 4), "peak": peak,
-        "peak_source": peak_src,
-        "reference_traffic_bytes_per_neuron_step": "8 fwd + 8 (u rebuild) + 12 (sums) + 16 (input grad) = 44"}))
+    L, sp, P = _capi.lib(), _capi._stream(dev), _capi._ptr
+    for layout, inner, shape, dims in (("contiguous [T,B,C,H,W], inner = H*W", HW, (T, B, C, 32, 32), (0, 1, 3, 4)),
+                                       ("channels-last [T,B,H,W,C], inner = 1", 1, (T, B, 32, 32, C), (0, 1, 2, 3))):
+        gen = torch.Generator(device=dev).manual_seed(1234)
+        x = torch.randn(shape, device=dev, generator=gen) * 1.5 + 0.3
+        g = torch.randn(shape, device=dev, generator=gen)
+        w = torch.rand(C, device=dev, generator=gen) + 0.5
+        b = torch.randn(C, device=dev, generator=gen) * 0.2
+        var, mean = torch.var_mean(x, dim=dims, unbiased=False)
+        out, gx = torch.empty_like(x), torch.empty_like(x)
+        ivar = torch.empty_like(w)
+        sums = torch.empty((2, C), device=dev)
+        means = torch.empty((2, C), device=dev)
+        fwd = lambda: L.snn_bn_lif_fwd(P(x), P(w), P(b), P(var), P(mean), 1e-5, P(out), None, P(ivar), T, N, C, inner, 0, 1,
+                                       ALPHA, THRESH, sp)
+        assert fwd() == 0
+
+        def bwd():
+            rc = L.snn_bn_lif_bwd_sums(P(x), P(g), P(w), P(b), P(ivar), P(mean), P(sums[0]), P(sums[1]), T, N, C, inner, 0, 1,
+                                       ALPHA, THRESH, BETA, INTERVAL, sp)
+            rc |= L.snn_bn_channel_means(P(sums[0]), P(sums[1]), P(w), P(means[0]), P(means[1]), C, float(T * N // C), sp)
+            rc |= L.snn_bn_lif_bwd_input(P(x), P(g), P(w), P(b), P(ivar), P(mean), P(means[0]), P(means[1]), P(gx), T, N, C,
+                                         inner, 0, 1, ALPHA, THRESH, BETA, INTERVAL, sp)
+            assert rc == 0
+
+        def sums_only():
+            assert L.snn_bn_lif_bwd_sums(P(x), P(g), P(w), P(b), P(ivar), P(mean), P(sums[0]), P(sums[1]), T, N, C, inner, 0, 1,
+                                         ALPHA, THRESH, BETA, INTERVAL, sp) == 0
+        reps = args.steps if args.steps < 50 else 20
+        t_f, t_b, t_s = _time_kernel(fwd, reps), _time_kernel(bwd, reps), _time_kernel(sums_only, reps)
+        gb = lambda nbytes, ms: nbytes * T * N / ms / 1e6
+        print(json.dumps({
+            "metric": "bn_lif_fwd_bwd_hbm_gbps", "value": round(gb(28, t_f + t_b), 1), "unit": "GB/s", "dtype": "f32",
+            "config": {"workload": f"bn_fire fwd + 2-pass bwd fp32 T=8 B={B} C=256 32x32 N=2^{args.log2n}, {layout}",
+                       "bytes_per_neuron_step": "fwd 8, bwd sums pass 8 + input pass 12",
+                       "l2": "working set > L2"},
+            "fwd_ms": round(t_f, 4), "fwd_gbs": round(gb(8, t_f), 1), "bwd_ms": round(t_b, 4),
+            "bwd_gbs": round(gb(20, t_b), 1), "bwd_sums_pass_ms": round(t_s, 4), "bwd_sums_pass_gbs": round(gb(8, t_s), 1),
+            "frac_of_peak": round(gb(28, t_f + t_b) / peak, 4), "peak": peak, "peak_source": peak_src,
+            "reference_traffic_bytes_per_neuron_step": "8 fwd + 8 (u rebuild) + 12 (sums) + 16 (input grad) = 44"}))
+        del x, g, out, gx
 
 
 def bf16_peak_tflops():

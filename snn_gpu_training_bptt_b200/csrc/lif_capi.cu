@@ -4,6 +4,8 @@
 #include "../../include/snn_b200.h"
 #include "lif_kernels.cuh"
 
+#include <stdlib.h>
+
 #include <type_traits>
 
 namespace {
@@ -95,7 +97,12 @@ inline Tune bwd_tune(int dtype, int tmax) {
     switch (dtype) {
         case SNN_F32: return {2, tmax >= 32 ? 128 : 256};
         case SNN_F64: return {tmax <= 16 ? 2 : 1, tmax >= 24 ? 128 : 256};
-        default: return {tmax <= 8 ? 8 : (tmax <= 16 ? 4 : 2), 128};
+        default: {
+            // 16-bit I/O: 16-byte accesses (8 neurons per thread) while the time axis is short, 8-byte
+            // accesses from `wide_t` steps on. SNN_LIF_BWD_WIDE_T overrides the switch point (a tuning aid).
+            static const int wide_t = [] { const char* e = getenv("SNN_LIF_BWD_WIDE_T"); return e ? atoi(e) : 6; }();
+            return {tmax <= wide_t ? 8 : (tmax <= 16 ? 4 : 2), 128};
+        }
     }
 }
 
@@ -164,14 +171,21 @@ void launch_bwd_regs(int vec, int block, const void* x, const void* g, void* gx,
                      float alpha, float thresh, float beta, float interval, cudaStream_t st) {
     // VEC * TMAX state words per thread stay in registers: cap the width for long time axes
     constexpr int kIoMax = 16 / static_cast<int>(sizeof(IO));
-    constexpr int kWords = TMAX <= 8 ? 8 : (TMAX <= 16 ? 4 : 2);
+    // 16-bit I/O keeps 16-byte accesses (8 neurons) up to 16 steps: the inputs sit in registers as
+    // packed pairs, so 8 x 16 fp32 membrane values + 2 x 64 packed words still fit (214 registers)
+    constexpr int kWords = TMAX <= 8 ? 8 : (TMAX <= 16 ? (sizeof(IO) == 2 ? 8 : 4) : 2);
     constexpr int kRegMax = kWords * 4 / static_cast<int>(sizeof(typename snn::Elem<IO>::CT));
     constexpr int kMaxVec = kIoMax < kRegMax ? kIoMax : kRegMax;
     with_vec<kMaxVec>(vec, [&](auto v) {
         constexpr int VEC = decltype(v)::value;
-        snn::lif_bwd_kernel<IO, VEC, TMAX><<<grid_for(N, VEC, block), block, 0, st>>>(
-            static_cast<const IO*>(x), static_cast<const IO*>(g), static_cast<IO*>(gx), T, N, alpha,
-            thresh, beta, interval);
+        if (T == TMAX)
+            snn::lif_bwd_kernel<IO, VEC, TMAX, true><<<grid_for(N, VEC, block), block, 0, st>>>(
+                static_cast<const IO*>(x), static_cast<const IO*>(g), static_cast<IO*>(gx), T, N, alpha,
+                thresh, beta, interval);
+        else
+            snn::lif_bwd_kernel<IO, VEC, TMAX, false><<<grid_for(N, VEC, block), block, 0, st>>>(
+                static_cast<const IO*>(x), static_cast<const IO*>(g), static_cast<IO*>(gx), T, N, alpha,
+                thresh, beta, interval);
     });
 }
 

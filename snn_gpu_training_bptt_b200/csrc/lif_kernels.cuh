@@ -150,6 +150,19 @@ __device__ __forceinline__ void st_stream(E* p, const Pack<E, VEC>& v) {
     }
 }
 
+// Makes every word of a freshly loaded pack an operand of an (empty) volatile statement placed
+// right after the load loops: the loads cannot be sunk below it. Used by the 16-bit backward,
+// where the compiler otherwise postpones the gradient loads until after the forward recurrence to
+// save registers and their latency is exposed (measured: 4.6 instead of 6.4 TB/s at T=8).
+template <typename P>
+__device__ __forceinline__ void keep_loaded(P& p) {
+    if constexpr (sizeof(P) >= 4) {
+        unsigned int* w = reinterpret_cast<unsigned int*>(&p);
+#pragma unroll
+        for (int i = 0; i < static_cast<int>(sizeof(P) / 4); ++i) asm volatile("" : "+r"(w[i]));
+    }
+}
+
 // ---------------------------------------------------------------------------------------
 // Forward. Runtime T walked in chunks of TC steps: the TC loads of a chunk are issued
 // before any of them is consumed. Outputs, each skipped when its pointer is null (the
@@ -251,6 +264,11 @@ __device__ __forceinline__ void lif_bwd_body(const IO* __restrict__ x, const IO*
 #pragma unroll
     for (int t = 0; t < TMAX; ++t)
         if (EXACT || t < T) gin[t] = ld_stream<IO, VEC>(g + static_cast<int64_t>(t) * N + i);
+    if constexpr (sizeof(IO) == 2) {
+#pragma unroll
+        for (int t = 0; t < TMAX; ++t)
+            if (EXACT || t < T) { keep_loaded(xin[t]); keep_loaded(gin[t]); }
+    }
 
     CT u[TMAX][VEC];
     {
@@ -295,20 +313,16 @@ __device__ __forceinline__ void lif_bwd_body(const IO* __restrict__ x, const IO*
 }
 
 // ---------------------------------------------------------------------------------------
-// T == TMAX (the common case: 4, 6, 8, 12, 16 steps) runs without per-step bound checks.
-template <typename IO, int VEC, int TMAX>
+// EXACT = (T == TMAX), chosen by the host (the common case: 4, 6, 8, 12, 16 steps): that
+// instantiation carries no per-step bound checks. Two kernels instead of two bodies in one keep
+// each at its own register count (16-bit I/O at 16 steps: 8 neurons x 16 steps of state per thread).
+template <typename IO, int VEC, int TMAX, bool EXACT>
 __global__ void
 lif_bwd_kernel(const IO* __restrict__ x, const IO* __restrict__ g,
                IO* __restrict__ gx, int T, int64_t N, float alpha_f,
                float thresh_f, float beta_f, float interval_f)
 {
-    // Two bodies in one kernel cost registers; where that drops a resident block (16-bit I/O,
-    // 4 x 16 values per thread: 114 -> 140 registers) only the checked body is compiled.
-    constexpr bool kSpecialise = !(sizeof(IO) == 2 && VEC * TMAX >= 64 && TMAX >= 16);
-    if (kSpecialise && T == TMAX)
-        lif_bwd_body<IO, VEC, TMAX, true>(x, g, gx, T, N, alpha_f, thresh_f, beta_f, interval_f);
-    else
-        lif_bwd_body<IO, VEC, TMAX, false>(x, g, gx, T, N, alpha_f, thresh_f, beta_f, interval_f);
+    lif_bwd_body<IO, VEC, TMAX, EXACT>(x, g, gx, T, N, alpha_f, thresh_f, beta_f, interval_f);
 }
 
 

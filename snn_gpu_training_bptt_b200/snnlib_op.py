@@ -101,7 +101,7 @@ class _BnStats(nn.Module):
             var = moments[1] / self.world_size - mean ** 2
         elif low:
             mean = self._mean32(x)
-            var = (self._mean_sq32(x) - mean ** 2).clamp_(min=0.0)
+            var = (self._mean_sq32(x) - mean ** 2).clamp(min=0.0)
         else:
             var, mean = torch.var_mean(x, dim=self.dim_bn, unbiased=False)
         m = self._momentum
@@ -119,7 +119,7 @@ class _BnStats(nn.Module):
         if x.dtype == torch.float32:
             return torch.mean(x * x, dim=self.dim_bn)
         count = x.numel() / self._bn_channels
-        return torch.linalg.vector_norm(x, 2, dim=self.dim_bn, dtype=torch.float32).square_().div_(count)
+        return torch.linalg.vector_norm(x, 2, dim=self.dim_bn, dtype=torch.float32).square() / count
 
 
 class Bn(_BnStats):
