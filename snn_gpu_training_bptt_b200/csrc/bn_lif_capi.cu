@@ -173,9 +173,46 @@ int snn_bn_lif_bwd_sums(const void* x, const void* grad, const float* weight, co
             *nq = static_cast<int>(runs < C ? runs : C);             // more runs than channels: one slot per channel
             return 2 * sizeof(float) * static_cast<size_t>(*nq);
         };
+        // runs of one neuron whose channels repeat with the CTA span: few fat CTAs, one flush each
+        auto short_runs = [&](int VEC) {
+            return inner == 1 && (static_cast<long long>(kBlock) * VEC) % C == 0 && Ni % VEC == 0 && C <= 4096;
+        };
+        auto fat_grid = [&](int VEC) {
+            const long long slabs = (Ni + static_cast<long long>(kBlock) * VEC - 1) / (static_cast<long long>(kBlock) * VEC);
+            int dev = 0, sms = 148;
+            if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+            const long long want = static_cast<long long>(sms) * 8;
+            return static_cast<unsigned>(slabs < want ? slabs : want);
+        };
+        // long runs: a grid that is a multiple of C, every CTA stays on one channel (see the kernel)
+        const long long runs = Ni / inner;                       // channel runs in the tensor: (T*)B*C
+        auto long_runs = [&](int VEC) {
+            return inner >= static_cast<long long>(kBlock) * VEC && inner % VEC == 0 && runs / C >= 1;
+        };
+        auto run_grid = [&]() {
+            int dev = 0, sms = 148;
+            if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+            long long k = (static_cast<long long>(sms) * 8 + C - 1) / C;     // CTAs per channel
+            const long long per_channel = runs / C;                          // visits available per channel
+            if (k > per_channel) k = per_channel;
+            if (k < 1) k = 1;
+            return static_cast<unsigned>(k * C);
+        };
         if (!fire) {
             with_vec4(vec, [&](auto v) {
                 constexpr int VEC = decltype(v)::value;
+                if (long_runs(VEC)) {
+                    snn::bn_lif_bwd_sums_run_kernel<IO, VEC, 2, false><<<run_grid(), kBlock, 0, st>>>(
+                        static_cast<const IO*>(x), static_cast<const IO*>(grad), sum_g, sum_gx, p, Ti, Ni, runs, alpha,
+                        thresh, beta, interval);
+                    return;
+                }
+                if (short_runs(VEC)) {
+                    snn::bn_lif_bwd_sums_cl_kernel<IO, VEC, 2, false><<<fat_grid(VEC), kBlock, 2 * sizeof(float) * C, st>>>(
+                        static_cast<const IO*>(x), static_cast<const IO*>(grad), sum_g, sum_gx, p, Ti, Ni, alpha, thresh,
+                        beta, interval);
+                    return;
+                }
                 int nq; const size_t smem = smem_for(VEC, &nq);
                 if (inner % (32 * VEC) == 0)
                     snn::bn_lif_bwd_sums_kernel<IO, VEC, 2, false, true><<<grid_for(Ni, VEC), kBlock, 0, st>>>(
@@ -192,6 +229,18 @@ int snn_bn_lif_bwd_sums(const void* x, const void* grad, const float* weight, co
             constexpr int TMAX = decltype(tm)::value;
             with_vec4(vec < max_vec<TMAX>() ? vec : max_vec<TMAX>(), [&](auto v) {
                 constexpr int VEC = decltype(v)::value < max_vec<TMAX>() ? decltype(v)::value : max_vec<TMAX>();
+                if (long_runs(VEC)) {
+                    snn::bn_lif_bwd_sums_run_kernel<IO, VEC, TMAX, true><<<run_grid(), kBlock, 0, st>>>(
+                        static_cast<const IO*>(x), static_cast<const IO*>(grad), sum_g, sum_gx, p, Ti, Ni, runs, alpha,
+                        thresh, beta, interval);
+                    return;
+                }
+                if (short_runs(VEC)) {
+                    snn::bn_lif_bwd_sums_cl_kernel<IO, VEC, TMAX, true><<<fat_grid(VEC), kBlock, 2 * sizeof(float) * C, st>>>(
+                        static_cast<const IO*>(x), static_cast<const IO*>(grad), sum_g, sum_gx, p, Ti, Ni, alpha, thresh,
+                        beta, interval);
+                    return;
+                }
                 int nq; const size_t smem = smem_for(VEC, &nq);
                 if (inner % (32 * VEC) == 0)
                     snn::bn_lif_bwd_sums_kernel<IO, VEC, TMAX, true, true><<<grid_for(Ni, VEC), kBlock, 0, st>>>(

@@ -63,7 +63,12 @@ def make_case(shape, seed, C=None):
 
 
 SHAPES = [(6, 2, 8), (6, 2, 8, 8, 8), (8, 3, 5, 7, 3), (4, 4, 16, 1, 1), (1, 2, 3, 2, 2), (12, 2, 6, 5, 5),
-          (16, 2, 130), (20, 1, 4, 3, 3), (32, 2, 8, 2, 2), (8, 8, 64, 16, 16)]
+          (16, 2, 130), (20, 1, 4, 3, 3), (32, 2, 8, 2, 2), (8, 8, 64, 16, 16),
+          # channel runs at least as long as a CTA's span (the one-channel-per-CTA sums kernel), one of
+          # them not a multiple of the span, one with more CTAs per channel than batch items
+          (8, 3, 5, 32, 32), (4, 2, 3, 24, 24), (6, 1, 4, 40, 40),
+          # runs of one neuron with C dividing the CTA span (the fixed-channel sums kernel) and not
+          (8, 64, 128), (6, 24, 48)]
 
 
 @pytest.mark.parametrize("shape", SHAPES)
@@ -119,6 +124,24 @@ def test_channels_last_and_bf16(capi):
     gx_ref, gw_ref, gb_ref, _, _ = orc.c_bn_lif_bwd(xb.float(), gb16.float(), w, b, ivar_ref, mean_b)
     gx, gw, gbias = snnlib.bn_fire_bp(xb.cuda(), P[0], P[1], ivar_b, mean_b.cuda(), None, gb16.cuda(), A, TH, BE, IV)
     close(gx, gx_ref, 1e-2, "bf16 grad_x"); close(gw, gw_ref, 1e-4, "bf16 grad_w"); close(gbias, gb_ref, 1e-4, "bf16 grad_b")
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("shape", [(8, 2, 6, 32, 32), (16, 2, 4, 32, 48), (8, 32, 256)])
+def test_sums_kernels_for_long_and_short_runs_in_16_bit(capi, dtype, shape):
+    """The per-channel sums of the 16-bit backward on the layouts that take the fat-CTA kernels
+    (long runs: 4 neurons per thread; [T, B, C]: fixed channels per thread) against the oracle run
+    in fp32 on the rounded inputs."""
+    from snn_gpu_training_bptt_b200 import snnlib
+    x, g, w, b, _, _ = make_case(shape, seed=sum(shape) + 5)
+    x16, g16 = x.to(dtype), g.to(dtype)
+    dims = (0, 1) if len(shape) == 3 else (0, 1, 3, 4)
+    var, mean = torch.var_mean(x16.float(), dim=dims, unbiased=False)
+    ivar_ref, _, _ = orc.c_bn_lif_fwd(x16.float(), w, b, var, mean, EPS)
+    gx_ref, gw_ref, gb_ref, _, _ = orc.c_bn_lif_bwd(x16.float(), g16.float(), w, b, ivar_ref, mean)
+    ivar = torch.from_numpy(np.asarray(ivar_ref)).cuda()
+    gx, gw, gb = snnlib.bn_fire_bp(x16.cuda(), w.cuda(), b.cuda(), ivar, mean.cuda(), None, g16.cuda(), A, TH, BE, IV)
+    close(gw, gw_ref, 1e-4, "grad_w"); close(gb, gb_ref, 1e-4, "grad_b"); close(gx, gx_ref, 1e-2, "grad_x")
 
 
 def test_sync_bn_split_matches_one_shot(capi):
