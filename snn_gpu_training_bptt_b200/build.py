@@ -59,5 +59,28 @@ def build(force: bool = False, verbose: bool = False) -> str:
     return LIB
 
 
+WAIT_TEST_LIB = os.path.join(PKG, "libsnn_b200_waittest.so")
+
+
+def build_wait_test(force: bool = False) -> str:
+    """Test-only variant of the library (used by one GPU test, never by the package): every bounded
+    wait of the tcgen05 kernels limited to ~10 ms and a hook that makes the persistent forward
+    kernel's producer skip one K stage, so the expiry path can be exercised."""
+    build()                                   # the ordinary objects are reused for everything else
+    src = os.path.join(CSRC, "linear_lif_tcgen05.cu")
+    if (not force and os.path.exists(WAIT_TEST_LIB)
+            and os.path.getmtime(WAIT_TEST_LIB) >= max(os.path.getmtime(src), os.path.getmtime(LIB))):
+        return WAIT_TEST_LIB
+    nvcc = os.environ.get("NVCC", "nvcc")
+    objdir = os.path.join(PKG, "build")
+    obj = os.path.join(objdir, "linear_lif_tcgen05_waittest.o")
+    flags = [f for f in NVCC_FLAGS if f != "-shared"] + ["-DSNN_TC_WAIT_TEST", "-DSNN_TC_WAIT_CYCLES=20000000LL"]
+    subprocess.run([nvcc] + flags + ["-c", "-o", obj, src], check=True)
+    others = [os.path.join(objdir, os.path.basename(s)[:-3] + ".o") for s in sources() if s != src]
+    subprocess.run([nvcc, "-shared", "-gencode", "arch=compute_100a,code=sm_100a", "-o", WAIT_TEST_LIB, obj] + others,
+                   check=True)
+    return WAIT_TEST_LIB
+
+
 if __name__ == "__main__":
     print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv))

@@ -333,7 +333,7 @@ bwd_gemm_kernel(const __grid_constant__ GemmParams P)
                 for (int rb = 0; rb < pr.num_rb; ++rb, ++it) {
                     const int s = it % GSTAGES;
                     const uint32_t parity = ((it / GSTAGES) & 1) ^ 1;      // first pass: slots start empty
-                    if (!mbar_wait(&sm.empty[s], parity)) { record_error(21); ok = false; break; }
+                    if (!mbar_wait(&sm.empty[s], parity, kDependentWaitCycles)) { record_error(21); ok = false; break; }
                     mbar_expect_tx(&sm.full[s], kStageA + kStageB);
                     const int r0 = rb * BR;
                     unsigned char* a = reinterpret_cast<unsigned char*>(sm.a[s]);
@@ -361,7 +361,7 @@ bwd_gemm_kernel(const __grid_constant__ GemmParams P)
                 constexpr uint32_t b_step = (16 * 128) >> 4;
                 const int buf = local & 1;
                 const uint32_t acc_parity = ((local >> 1) & 1) ^ 1;        // first use of a buffer passes
-                if (!mbar_wait(&sm.acc_empty[buf], acc_parity)) { record_error(24); break; }
+                if (!mbar_wait(&sm.acc_empty[buf], acc_parity, kDependentWaitCycles)) { record_error(24); break; }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint32_t tmem_acc = tmem_base + buf * TJ;
                 for (int rb = 0; rb < pr.num_rb; ++rb, ++it) {
@@ -403,13 +403,13 @@ bwd_gemm_kernel(const __grid_constant__ GemmParams P)
             const int buf = local & 1;
             const uint32_t acc_parity = (local >> 1) & 1;
             if (elected) {
-                const bool ok0 = mbar_wait(&sm.acc_full[buf], acc_parity);
+                const bool ok0 = mbar_wait(&sm.acc_full[buf], acc_parity, kDependentWaitCycles);
                 if (!ok0) record_error(23);
                 sm.epi_ok[g] = ok0 ? 1u : 0u;
             }
             group_barrier(g);
             if (sm.epi_ok[g] == 0u) break;
-            mbar_wait(&sm.acc_full[buf], acc_parity);     // already complete: returns at once, orders this thread
+            mbar_wait(&sm.acc_full[buf], acc_parity, kDependentWaitCycles);     // already complete: returns at once, orders this thread
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             if (elected && g == 0 && local < 2) SNN_TC_STAMP(50 + 2 * local);
 
@@ -520,7 +520,7 @@ bwd_gemm_pair_kernel(const __grid_constant__ GemmParams P)
                 for (int rb = 0; rb < pr.num_rb; ++rb, ++it) {
                     const int s = it % GPSTAGES;
                     const uint32_t parity = ((it / GPSTAGES) & 1) ^ 1;
-                    if (!mbar_wait(&sm.empty[s], parity)) { record_error(31); ok = false; break; }
+                    if (!mbar_wait(&sm.empty[s], parity, kDependentWaitCycles)) { record_error(31); ok = false; break; }
                     const uint32_t full_leader = mapa_shared(smem_u32(&sm.full[s]), 0);
                     if (leader) mbar_expect_tx(&sm.full[s], 2 * (kStageA + kPairStageB));
                     const int r0 = rb * BR;
@@ -543,7 +543,7 @@ bwd_gemm_pair_kernel(const __grid_constant__ GemmParams P)
                 constexpr uint32_t b_step = (16 * 128) >> 4;
                 const int buf = local & 1;
                 const uint32_t acc_parity = ((local >> 1) & 1) ^ 1;
-                if (!mbar_wait(&sm.acc_empty[buf], acc_parity)) { record_error(34); break; }
+                if (!mbar_wait(&sm.acc_empty[buf], acc_parity, kDependentWaitCycles)) { record_error(34); break; }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint32_t tmem_acc = tmem_base + buf * TJ;
                 for (int rb = 0; rb < pr.num_rb; ++rb, ++it) {
@@ -586,13 +586,13 @@ bwd_gemm_pair_kernel(const __grid_constant__ GemmParams P)
             const int buf = local & 1;
             const uint32_t acc_parity = (local >> 1) & 1;
             if (elected) {
-                const bool ok0 = mbar_wait(&sm.acc_full[buf], acc_parity);
+                const bool ok0 = mbar_wait(&sm.acc_full[buf], acc_parity, kDependentWaitCycles);
                 if (!ok0) record_error(33);
                 sm.epi_ok[g] = ok0 ? 1u : 0u;
             }
             group_barrier(g);
             if (sm.epi_ok[g] == 0u) break;
-            mbar_wait(&sm.acc_full[buf], acc_parity);     // already complete: orders this thread
+            mbar_wait(&sm.acc_full[buf], acc_parity, kDependentWaitCycles);     // already complete: orders this thread
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             if (elected && g == 0 && local < 2) SNN_TC_STAMP(50 + 2 * local);
 

@@ -47,6 +47,13 @@ namespace {
 
 using namespace snn_tc;
 
+// Test-only build (-DSNN_TC_WAIT_TEST, never part of libsnn_b200.so): the producer of the persistent
+// kernel leaves out the loads of one K stage when told to, so that stage's operands never arrive,
+// the MMA issuer's bounded wait runs out and the kernel must return with error code 2.
+#ifdef SNN_TC_WAIT_TEST
+__device__ int g_tc_test_skip_stage = -1;
+#endif
+
 constexpr int BM = 128;            // output neurons per CTA (= TMEM lanes)
 constexpr int BN = 128;            // (t, b) pairs per CTA (= TMEM columns)
 constexpr int BK = 64;             // K elements per stage: 64 bf16 = one 128-byte swizzled row
@@ -107,7 +114,7 @@ linear_lif_fwd_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
             for (int kb = 0; kb < num_kb; ++kb) {
                 const int s = kb % STAGES;
                 const uint32_t parity = ((kb / STAGES) & 1) ^ 1;     // first pass: slots start empty
-                if (!mbar_wait(&sm.empty[s], parity)) { record_error(1); break; }
+                if (!mbar_wait(&sm.empty[s], parity, kDependentWaitCycles)) { record_error(1); break; }
                 mbar_expect_tx(&sm.full[s], kStageBytesA + kStageBytesB);
                 tma_load_2d(sm.a[s], &map_w, &sm.full[s], kb * BK, m0);
                 tma_load_3d(sm.b[s], &map_x, &sm.full[s], kb * BK, b0, 0);
@@ -136,7 +143,7 @@ linear_lif_fwd_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
         }
     } else {
         // ------------------------------ epilogue: LIF over the tile ---------------
-        bool ok = mbar_wait(&sm.accum_full, 0);
+        bool ok = mbar_wait(&sm.accum_full, 0, kDependentWaitCycles);
         if (!ok) record_error(3);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         if (ok) {
@@ -354,9 +361,12 @@ linear_lif_fwd_persistent_kernel(const __grid_constant__ CUtensorMap map_w, cons
                 const int m0 = (tile % tiles_m) * BM, b0 = (tile / tiles_m) * BT;
                 for (int kb = 0; kb < num_kb; ++kb, ++it) {
                     if (it < preloaded) continue;             // requested before the set-up sync
+#ifdef SNN_TC_WAIT_TEST
+                    if (it == g_tc_test_skip_stage) continue; // test build: these operands are never requested
+#endif
                     const int s = it % PSTAGES;
                     const uint32_t parity = ((it / PSTAGES) & 1) ^ 1;
-                    if (!mbar_wait(&sm.empty[s], parity)) { record_error(1); ok = false; break; }
+                    if (!mbar_wait(&sm.empty[s], parity, kDependentWaitCycles)) { record_error(1); ok = false; break; }
                     mbar_expect_tx(&sm.full[s], kStageBytesA + PersistentCfg<WN>::kStageBytesB);
                     tma_load_2d(sm.a[s], &map_w, &sm.full[s], kb * BK, m0);
                     tma_load_3d(sm.b[s], &map_x, &sm.full[s], kb * BK, b0, 0);
@@ -372,7 +382,7 @@ linear_lif_fwd_persistent_kernel(const __grid_constant__ CUtensorMap map_w, cons
             for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
                 const int buf = local & 1;
                 const uint32_t acc_parity = ((local >> 1) & 1) ^ 1;      // first use of a buffer passes
-                if (!mbar_wait(&sm.acc_empty[buf], acc_parity)) { record_error(4); break; }
+                if (!mbar_wait(&sm.acc_empty[buf], acc_parity, kDependentWaitCycles)) { record_error(4); break; }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint32_t tmem_acc = tmem_base + buf * WN;
                 for (int kb = 0; kb < num_kb; ++kb, ++it) {
@@ -402,13 +412,13 @@ linear_lif_fwd_persistent_kernel(const __grid_constant__ CUtensorMap map_w, cons
             const int buf = local & 1;
             const uint32_t acc_parity = (local >> 1) & 1;
             if (elected) {
-                const bool ok0 = mbar_wait(&sm.acc_full[buf], acc_parity);
+                const bool ok0 = mbar_wait(&sm.acc_full[buf], acc_parity, kDependentWaitCycles);
                 if (!ok0) record_error(3);
                 sm.epi_ok[g] = ok0 ? 1u : 0u;
             }
             group_barrier(g);
             if (sm.epi_ok[g] == 0u) break;
-            mbar_wait(&sm.acc_full[buf], acc_parity);     // already complete: returns at once, orders this thread
+            mbar_wait(&sm.acc_full[buf], acc_parity, kDependentWaitCycles);     // already complete: returns at once, orders this thread
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 
             const float bias_m = bias != nullptr ? bias[m0 + row] : 0.f;
@@ -528,7 +538,7 @@ linear_lif_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
                 for (int kb = 0; kb < num_kb; ++kb, ++it) {
                     const int s = it % PAIR_STAGES;
                     const uint32_t parity = ((it / PAIR_STAGES) & 1) ^ 1;
-                    if (!mbar_wait(&sm.empty[s], parity)) { record_error(11); ok = false; break; }
+                    if (!mbar_wait(&sm.empty[s], parity, kDependentWaitCycles)) { record_error(11); ok = false; break; }
                     const uint32_t full_leader = mapa_shared(smem_u32(&sm.full[s]), 0);
                     if (leader) mbar_expect_tx(&sm.full[s], 2 * (kStageBytesA + (PAIR_N / 2) * BK * 2));
                     tma_load_2d_pair(sm.a[s], &map_w, full_leader, kb * BK, m0);
@@ -545,7 +555,7 @@ linear_lif_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
             for (int tile = pair; tile < num_tiles && ok; tile += num_pairs, ++local) {
                 const int buf = local & 1;
                 const uint32_t acc_parity = ((local >> 1) & 1) ^ 1;      // first use of a buffer passes
-                if (!mbar_wait(&sm.acc_empty[buf], acc_parity)) { record_error(14); break; }
+                if (!mbar_wait(&sm.acc_empty[buf], acc_parity, kDependentWaitCycles)) { record_error(14); break; }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint32_t tmem_acc = tmem_base + buf * PAIR_N;
                 for (int kb = 0; kb < num_kb; ++kb, ++it) {
@@ -578,13 +588,13 @@ linear_lif_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
             const int buf = local & 1;
             const uint32_t acc_parity = (local >> 1) & 1;
             if (elected) {
-                const bool ok0 = mbar_wait(&sm.acc_full[buf], acc_parity);
+                const bool ok0 = mbar_wait(&sm.acc_full[buf], acc_parity, kDependentWaitCycles);
                 if (!ok0) record_error(13);
                 sm.epi_ok[g] = ok0 ? 1u : 0u;
             }
             group_barrier(g);
             if (sm.epi_ok[g] == 0u) break;
-            mbar_wait(&sm.acc_full[buf], acc_parity);     // already complete: orders this thread
+            mbar_wait(&sm.acc_full[buf], acc_parity, kDependentWaitCycles);     // already complete: orders this thread
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 
             const float bias_m = bias != nullptr ? bias[m0 + row] : 0.f;
@@ -789,6 +799,13 @@ int snn_linear_lif_fwd(const void* x, const void* weight, const float* bias, voi
         return launch_persistent<S, 128>(mw, mx, ms, mc, wc, bias, Bi, Ki, Mi, alpha, thresh, Ti, st);
     });
 }
+
+#ifdef SNN_TC_WAIT_TEST
+// test build only: K stage (counted over the CTA's whole tile list, >= 3) whose loads every producer skips; -1 = none
+int snn_test_skip_stage(int stage) {
+    return cudaMemcpyToSymbol(g_tc_test_skip_stage, &stage, sizeof(int)) == cudaSuccess ? SNN_OK : SNN_ERR_CUDA;
+}
+#endif
 
 int snn_linear_lif_error(int reset) {
     // the forward and the backward kernels keep an error word each; report the forward's first

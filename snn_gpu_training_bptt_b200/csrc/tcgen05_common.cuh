@@ -13,7 +13,16 @@
 
 namespace snn_tc {
 
-constexpr long long kWaitCycles = 2000000000LL;       // bound of every mbarrier wait, ~1 s
+// Bound of every mbarrier wait in SM cycles: ~1 s. The test-only build that checks the expiry path
+// (tests/test_linear_lif_gpu.py) shortens it with -DSNN_TC_WAIT_CYCLES=...
+#ifndef SNN_TC_WAIT_CYCLES
+#define SNN_TC_WAIT_CYCLES 2000000000LL
+#endif
+constexpr long long kWaitCycles = SNN_TC_WAIT_CYCLES;
+// Waits that depend on another role's progress (a free stage, a full or drained accumulator) get twice
+// the limit of the waits for operands: when operands never arrive, the operand wait is the one that
+// expires first and names the cause (dependent waits then stop early on seeing the error word).
+constexpr long long kDependentWaitCycles = 2 * kWaitCycles;
 
 // 0, or the code of the first bounded wait that expired in a kernel of this translation unit
 static __device__ int g_tc_error = 0;
@@ -54,12 +63,12 @@ __device__ __forceinline__ void record_error(int code) { atomicCAS(&g_tc_error, 
 // false if the barrier did not reach the phase within the limit, or if another role (of any CTA)
 // has already recorded a failure: dependent waits then return at once instead of running out
 // their own limit one after the other.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, long long limit = kWaitCycles) {
     if (mbar_try_wait(bar, parity)) return true;
     const long long t0 = clock64();
     for (uint32_t spins = 1;; ++spins) {
         if (mbar_try_wait(bar, parity)) return true;
-        if (clock64() - t0 > kWaitCycles) return false;
+        if (clock64() - t0 > limit) return false;
         if ((spins & 63u) == 0u && *reinterpret_cast<volatile int*>(&g_tc_error) != 0) return false;
     }
 }

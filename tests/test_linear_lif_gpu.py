@@ -283,3 +283,21 @@ def test_config3_bf16_path_against_the_fp32_reference(capi):
     print("config 3, bf16 tcgen05 path vs fp32 reference:", figures)
     assert flips < 5e-3, figures
     assert figures["grad_x_rel_l2"] < 0.05 and figures["grad_w_rel_l2"] < 0.05 and figures["grad_b_rel_l2"] < 0.05, figures
+
+
+def test_bounded_wait_expires_and_is_reported(capi):
+    """A starved K stage (test-only build: the producer skips one stage's loads, waits limited to
+    ~10 ms) makes the MMA issuer's wait run out: the kernel returns instead of hanging, the error
+    word holds the issuer's code 2 (the first failure, not the epilogue's later one) until it is
+    cleared, and the next ordinary launch in the same context gives the right spikes again."""
+    import json
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    out = subprocess.run([sys.executable, os.path.join(root, "tests", "wait_expiry_child.py")], cwd=root,
+                         capture_output=True, text=True, timeout=600)
+    assert out.returncode == 0, out.stdout[-2000:] + out.stderr[-2000:]
+    r = json.loads([l for l in out.stdout.splitlines() if l.startswith("{")][-1])
+    assert r["rc_good_before"] == 0 and r["err_good_before"] == 0
+    assert r["rc_starved"] == 0                      # the launch itself is fine; the failure is reported by the word
+    assert r["err_starved"] == 2 and r["err_still_set"] == 2 and r["err_after_clear"] == 0, r
+    assert r["starved_ms"] < 2000.0, r               # bounded: ~10 ms per wait, nowhere near a hang
+    assert r["rc_good_after"] == 0 and r["err_good_after"] == 0 and r["same_spikes_after"], r
