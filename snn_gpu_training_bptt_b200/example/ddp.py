@@ -79,7 +79,7 @@ class DistributedDataParallel(torch.nn.Module):
                 dist.broadcast(t.data, src=0, group=self.group)
 
     def _build_buckets(self, bucket_mb, tail_mb):
-        """``tail_mb``: the LAST bucket holds the parameters of the first layers, whose gradients
+        """``tail_mb`` (a number or a sequence of decreasing numbers): the LAST bucket holds the parameters of the first layers, whose gradients
         exist only when backward ends, so its all-reduce is the one nothing can hide. It is cut
         down to at most ``tail_mb`` megabytes (its other parameters become a bucket of their own
         that is ready earlier): measured on the VGG-style network at 2 GPUs, an 18 MB last bucket
@@ -100,8 +100,11 @@ class DistributedDataParallel(torch.nn.Module):
             size += nbytes
         if current:
             groups.append(current)
-        if groups and tail_mb is not None and len(groups[-1]) > 1:
-            tail_cap = int(tail_mb * 1024 * 1024)
+        caps = [] if tail_mb is None else ([tail_mb] if isinstance(tail_mb, (int, float)) else list(tail_mb))
+        for cap_mb in caps:             # several caps cut the tail repeatedly: (1.0, 0.03) -> ..., <= 1 MB, <= 30 KB
+            if not groups or len(groups[-1]) <= 1:
+                break
+            tail_cap = int(cap_mb * 1024 * 1024)
             last, tail, size = groups[-1], [], 0
             while len(last) > 1 and size + last[-1].numel() * last[-1].element_size() <= tail_cap:
                 size += last[-1].numel() * last[-1].element_size()
