@@ -15,9 +15,20 @@ read grad 4 + write grad_x 4). With N>1 GPUs every rank processes its own 2^26-n
 (the neuron/batch axis shards with no exchange), so the aggregate is weak scaling.
 
 Printed keys beyond the base contract:
-  roofline      dominant kernel (the backward, 12 B/step) against the measured HBM copy peak
-  cpu_baseline  the PyTorch-autograd port of the reference's CPU path, timed on this host
-  e2e           same metric through the host-buffer API (pinned host -> device -> host)
+  roofline          dominant kernel (the backward, 12 B/step) against the measured HBM copy peak
+  cpu_baseline      the reference's own CPU path (its gold_op.py from oracle/_ref/, else the port in
+                    oracle/), timed on this host's cores on a bounded sample
+  e2e               same metric through the host-buffer API (pinned host -> device -> host)
+  linear_lif        the fused synaptic linear + LIF layer (T=8, batch 256, 2048 -> 2048, bf16) forward and
+                    BPTT backward on the tcgen05 kernels: microseconds, TFLOP/s, fraction of the bf16 peak
+  trainer, trainer_resnet19
+                    spiking-CNN training samples/s (VGG-style T=8 batch 64/GPU; ResNet-19-style T=16 batch
+                    128/GPU), data-parallel over the N ranks, with the exposed all-reduce time at N > 1
+  timed_blocks      the K-step block is repeated until >= 1 s is timed; the median block is reported
+Flat scalar copies of the nested legs (linear_lif_*, trainer_*) sit at the top level too.
+
+Other workloads (single measurements, not the contract line): --workload sweep | bn_lif | linear_lif |
+host_link.  --impl reference times the reference's CPU implementation on the host cores.
 """
 import argparse
 import json
