@@ -627,7 +627,7 @@ struct Workspace {
 };
 Workspace workspace_layout(int64_t T, int64_t B, int64_t M) {
     Workspace w;
-    const int rb = du_tmax(T) <= 8 ? du_rows_per_block(8) : du_rows_per_block(16);
+    const int rb = du_rows_per_block(du_tmax(T));
     w.partial_rows = static_cast<int>((B + rb - 1) / rb);
     w.du_bytes = align_up(static_cast<size_t>(T) * B * M * 2, 256);
     w.partial_bytes = align_up(static_cast<size_t>(w.partial_rows) * M * 4, 256);
