@@ -111,3 +111,33 @@ def test_cpu_tensors_are_rejected(built_lib):
         snnlib.fire_s_fp(x, 0.25, 0.25)
     with pytest.raises(ValueError, match="CUDA"):
         snnlib.fire_bp(x, x, 0.25, 0.25, 1.0, 0.5)
+
+
+def test_linear_lif_backward_host_logic(built_lib):
+    """Support test and workspace size of the fused linear + LIF backward are host logic (no GPU):
+    bf16 only, T <= 16, at least 128 (t, b) rows, K and M multiples of 64; the workspace holds dU
+    (bf16 [T, B, M]) plus one fp32 row of bias partials per block of batch items, 256-byte aligned."""
+    from snn_gpu_training_bptt_b200 import _capi
+    L = _capi.lib()
+    ok = lambda T, B, K, M, dt=1: L.snn_linear_lif_bwd_supported(T, B, K, M, dt)
+    assert ok(8, 256, 2048, 2048) == 1 and ok(1, 128, 64, 128) == 1 and ok(16, 8, 64, 128) == 1
+    assert ok(8, 256, 2048, 2048, dt=0) == 0          # fp32 operands
+    assert ok(17, 256, 2048, 2048) == 0               # time axis beyond the register-resident reverse pass
+    assert ok(8, 8, 2048, 2048) == 0                  # 64 (t, b) rows: less than one tile
+    assert ok(8, 256, 2048 + 8, 2048) == 0 and ok(8, 256, 2048, 2048 + 32) == 0
+    assert ok(8, 256, 32, 2048) == 0 and ok(8, 256, 2048, 64) == 0
+    align = lambda v: (v + 255) // 256 * 256
+    for T, B, K, M, rows_per_block in ((8, 256, 2048, 2048, 16), (4, 100, 64, 192, 16), (16, 40, 128, 128, 8), (12, 24, 64, 256, 8)):
+        want = align(T * B * M * 2) + align(-(-B // rows_per_block) * M * 4)
+        assert L.snn_linear_lif_bwd_workspace_bytes(T, B, K, M, 1) == want, (T, B, K, M)
+    assert L.snn_linear_lif_bwd_workspace_bytes(8, 8, 2048, 2048, 1) < 0
+    # argument checks that need no device: nothing is launched on a non-zero status
+    assert L.snn_linear_lif_bwd(None, None, None, None, None, None, None, 8, 256, 2048, 2048, 0, 0,
+                                0.25, 0.25, 1.0, 0.5, None, 0, None) == 5
+    assert L.snn_linear_lif_bwd(None, None, None, None, None, None, None, 8, 256, 2048, 2048, 1, 2,
+                                0.25, 0.25, 1.0, 0.5, None, 0, None) == 3      # grad_weight dtype f16
+    assert L.snn_linear_lif_bwd(None, None, None, None, None, None, None, 8, 256, 2048, 2048, 1, 0,
+                                0.25, 0.25, 1.0, 0.5, None, 0, None) == 1      # current / grad_spike missing
+    assert L.snn_copy_rows_async(None, 16, None, 16, 16, 4, 1, None) == 1
+    assert L.snn_copy_rows_async(None, 16, None, 16, 16, 0, 1, None) == 0       # nothing to copy
+    assert L.snn_copy_rows_async(ctypes.c_void_p(256), 8, ctypes.c_void_p(512), 16, 16, 4, 1, None) == 2   # pitch < row
