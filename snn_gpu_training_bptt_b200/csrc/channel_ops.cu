@@ -48,6 +48,81 @@ __global__ void channel_bias_add_kernel(IO* __restrict__ y, const float* __restr
     snn::st_stream<IO, VEC>(y + i, v);
 }
 
+// Fixed-pattern variants for inner == 1 (channels-last images, [rows, C] matrices) with C dividing
+// kBlock * VEC: channel = n % C, so a thread that strides through the tensor in whole spans of
+// kBlock * VEC elements meets the same VEC consecutive channels every time. The bias values (or the
+// partial sums) of those channels stay in registers for the thread's whole walk; there is no
+// division per element and, for the sum, one shared-memory reduction and C global atomics per CTA
+// for the whole walk. The general kernels computed a division and a modulo per ELEMENT and were
+// issue-bound at 2.1 TB/s (bias add) and 2.4 TB/s (sum) on the trainer's bf16 tensors, together
+// 19 % of a training step. kUnroll vectors per thread are in flight at a time.
+constexpr int kUnroll = 4;
+
+template <typename IO, int VEC>
+__global__ void __launch_bounds__(kBlock)
+channel_bias_add_fixed_kernel(IO* __restrict__ y, const float* __restrict__ bias, long long total, int C)
+{
+    const int c0 = static_cast<int>((static_cast<long long>(threadIdx.x) * VEC) % C);
+    float b[VEC];
+#pragma unroll
+    for (int k = 0; k < VEC; ++k) b[k] = bias[c0 + k];         // C % VEC == 0: no wrap inside a vector
+    const long long span = static_cast<long long>(kBlock) * VEC;
+    const long long stride = static_cast<long long>(gridDim.x) * span;
+    long long i = static_cast<long long>(blockIdx.x) * span + static_cast<long long>(threadIdx.x) * VEC;
+    for (; i + (kUnroll - 1) * stride < total; i += kUnroll * stride) {
+        snn::Pack<IO, VEC> v[kUnroll];
+#pragma unroll
+        for (int u = 0; u < kUnroll; ++u) v[u] = snn::ld_stream<IO, VEC>(y + i + u * stride);
+#pragma unroll
+        for (int u = 0; u < kUnroll; ++u) {
+#pragma unroll
+            for (int k = 0; k < VEC; ++k)
+                v[u].v[k] = snn::Elem<IO>::store(snn::add_rn(snn::Elem<IO>::load(v[u].v[k]), b[k]));
+            snn::st_stream<IO, VEC>(y + i + u * stride, v[u]);
+        }
+    }
+    for (; i < total; i += stride) {
+        snn::Pack<IO, VEC> v = snn::ld_stream<IO, VEC>(y + i);
+#pragma unroll
+        for (int k = 0; k < VEC; ++k) v.v[k] = snn::Elem<IO>::store(snn::add_rn(snn::Elem<IO>::load(v.v[k]), b[k]));
+        snn::st_stream<IO, VEC>(y + i, v);
+    }
+}
+
+template <typename IO, int VEC>
+__global__ void __launch_bounds__(kBlock)
+channel_sum_fixed_kernel(const IO* __restrict__ g, float* __restrict__ out, long long total, int C)
+{
+    extern __shared__ float sacc[];
+    for (int j = threadIdx.x; j < C; j += blockDim.x) sacc[j] = 0.f;
+    __syncthreads();
+    float acc[VEC];
+#pragma unroll
+    for (int k = 0; k < VEC; ++k) acc[k] = 0.f;
+    const long long span = static_cast<long long>(kBlock) * VEC;
+    const long long stride = static_cast<long long>(gridDim.x) * span;
+    long long i = static_cast<long long>(blockIdx.x) * span + static_cast<long long>(threadIdx.x) * VEC;
+    for (; i + (kUnroll - 1) * stride < total; i += kUnroll * stride) {
+        snn::Pack<IO, VEC> v[kUnroll];
+#pragma unroll
+        for (int u = 0; u < kUnroll; ++u) v[u] = snn::ld_stream<IO, VEC>(g + i + u * stride);
+#pragma unroll
+        for (int u = 0; u < kUnroll; ++u)
+#pragma unroll
+            for (int k = 0; k < VEC; ++k) acc[k] += snn::Elem<IO>::load(v[u].v[k]);
+    }
+    for (; i < total; i += stride) {
+        const snn::Pack<IO, VEC> v = snn::ld_stream<IO, VEC>(g + i);
+#pragma unroll
+        for (int k = 0; k < VEC; ++k) acc[k] += snn::Elem<IO>::load(v.v[k]);
+    }
+    const int c0 = static_cast<int>((static_cast<long long>(threadIdx.x) * VEC) % C);
+#pragma unroll
+    for (int k = 0; k < VEC; ++k) atomicAdd(&sacc[c0 + k], acc[k]);
+    __syncthreads();
+    for (int j = threadIdx.x; j < C; j += blockDim.x) atomicAdd(&out[j], sacc[j]);
+}
+
 // out[c] += sum over all elements of channel c. Each CTA owns a contiguous span of
 // kBlock*VEC*kIter elements and accumulates per channel in shared memory (one slot per channel;
 // SMEM=false for very wide layers: straight to global atomics), then issues one global atomicAdd
@@ -152,6 +227,20 @@ inline int geometry_ok(int64_t outer, int64_t C, int64_t inner, int dtype) {
     return SNN_OK;
 }
 
+// channels repeat with the CTA span and never wrap inside a vector
+inline bool fixed_pattern(int64_t inner, int64_t C, int vec, long long total) {
+    return inner == 1 && C % vec == 0 && (static_cast<long long>(kBlock) * vec) % C == 0 && total % vec == 0;
+}
+// a few CTAs per SM, each walking the tensor in strides of the whole grid
+inline unsigned fat_grid(long long total, int vec) {
+    int dev = 0, sms = 148;
+    if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    const long long span = static_cast<long long>(kBlock) * vec;
+    const long long spans = (total + span - 1) / span;
+    const long long want = static_cast<long long>(sms) * 8;
+    return static_cast<unsigned>(spans < want ? spans : want);
+}
+
 inline int launch_status() {
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) { snn_internal::set_last_cuda_error(static_cast<int>(e)); return SNN_ERR_CUDA; }
@@ -176,6 +265,11 @@ int snn_channel_bias_add(void* y, const float* bias, int64_t outer, int64_t C, i
     dispatch(dtype, vec, [&](auto io, auto v) {
         using IO = decltype(io);
         constexpr int VEC = decltype(v)::value;
+        if (fixed_pattern(inner, C, VEC, total)) {
+            channel_bias_add_fixed_kernel<IO, VEC><<<fat_grid(total, VEC), kBlock, 0, st>>>(
+                static_cast<IO*>(y), bias, total, static_cast<int>(C));
+            return;
+        }
         const long long threads = (total + VEC - 1) / VEC;
         channel_bias_add_kernel<IO, VEC><<<static_cast<unsigned>((threads + kBlock - 1) / kBlock), kBlock, 0, st>>>(
             static_cast<IO*>(y), bias, total, inner, static_cast<int>(C));
@@ -200,6 +294,11 @@ int snn_channel_sum(const void* grad, float* out, int64_t outer, int64_t C, int6
     dispatch(dtype, vec, [&](auto io, auto v) {
         using IO = decltype(io);
         constexpr int VEC = decltype(v)::value;
+        if (fixed_pattern(inner, C, VEC, total) && C <= 8192) {
+            channel_sum_fixed_kernel<IO, VEC><<<fat_grid(total, VEC), kBlock, sizeof(float) * C, st>>>(
+                static_cast<const IO*>(grad), out, total, static_cast<int>(C));
+            return;
+        }
         const long long span = static_cast<long long>(kBlock) * VEC * kIter;
         const long long blocks = (total + span - 1) / span;
         const int same = (inner == 1 && (static_cast<long long>(kBlock) * VEC) % C == 0) ? 1 : 0;

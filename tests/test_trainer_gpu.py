@@ -244,7 +244,9 @@ def test_channel_bias_add_and_sum_kernels(dtype):
     from snn_gpu_training_bptt_b200 import _capi
     gen = torch.Generator().manual_seed(0)
     cases = [((512, 128, 8, 8), True), ((512, 128, 8, 8), False), ((37, 5, 3, 7), False), ((37, 6, 3, 7), True),
-             ((2048, 1024), False), ((33, 9000), False), ((3, 7), False), ((64, 96, 4, 4), True)]
+             ((2048, 1024), False), ((33, 9000), False), ((3, 7), False), ((64, 96, 4, 4), True),
+             # large enough for the fixed-pattern kernels' unrolled walk (several strides of the whole grid) and its ragged tail
+             ((520, 128, 16, 16), True), ((4097, 512), False)]
     for shape, channels_last in cases:
         y = torch.randn(shape, generator=gen).to(dtype).cuda()
         if channels_last:
