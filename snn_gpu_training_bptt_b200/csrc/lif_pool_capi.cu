@@ -74,7 +74,8 @@ int snn_lif_pool_fwd(const void* x, void* out, int64_t T, int64_t B, int64_t H, 
     if (B == 0) return SNN_OK;
     if (!x || !out) return SNN_ERR_NULL;
     if (!aligned(x, es) || !aligned(out, es)) return SNN_ERR_ALIGN;
-    const int vec = pick_vec(C, es, {x, out});
+    int vec = pick_vec(C, es, {x, out});
+    if (T > 8 && dtype == SNN_F32 && vec > 2) vec = 2;      // 4 windows x 16 steps of loads stay in registers
     const long long threads = B * (H / 2) * (W / 2) * (C / vec);
     if ((threads + kBlock - 1) / kBlock > 0x7fffffffLL) return SNN_ERR_SHAPE;
     const unsigned grid = static_cast<unsigned>((threads + kBlock - 1) / kBlock);
@@ -98,14 +99,16 @@ int snn_lif_pool_bwd(const void* x, const void* grad_out, void* grad_x, int64_t 
     if (!x || !grad_out || !grad_x) return SNN_ERR_NULL;
     if (!aligned(x, es) || !aligned(grad_out, es) || !aligned(grad_x, es)) return SNN_ERR_ALIGN;
     int vec = pick_vec(C, es, {x, grad_out, grad_x});
-    if (T > 8 && dtype == SNN_F32 && vec > 2) vec = 2;      // keep 16 steps of fp32 state in registers
+    if (T > 8 && vec > 2) vec = 2;                          // 4 windows x 16 steps of loads + 16 steps of state in registers
     const long long threads = B * (H / 2) * (W / 2) * (C / vec);
-    if ((threads + kBlock - 1) / kBlock > 0x7fffffffLL) return SNN_ERR_SHAPE;
-    const unsigned grid = static_cast<unsigned>((threads + kBlock - 1) / kBlock);
+    // 128-thread CTAs: at ~160 registers per thread three of them fit an SM, one 256-thread CTA would not
+    constexpr int kBwdBlock = 128;
+    if ((threads + kBwdBlock - 1) / kBwdBlock > 0x7fffffffLL) return SNN_ERR_SHAPE;
+    const unsigned grid = static_cast<unsigned>((threads + kBwdBlock - 1) / kBwdBlock);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     dispatch(dtype, vec, static_cast<int>(T), [&](auto io, auto v, auto tm) {
         using IO = decltype(io);
-        snn::lif_pool_bwd_kernel<IO, decltype(v)::value, decltype(tm)::value><<<grid, kBlock, 0, st>>>(
+        snn::lif_pool_bwd_kernel<IO, decltype(v)::value, decltype(tm)::value><<<grid, kBwdBlock, 0, st>>>(
             static_cast<const IO*>(x), static_cast<const IO*>(grad_out), static_cast<IO*>(grad_x),
             static_cast<int>(T), static_cast<int>(B), static_cast<int>(H), static_cast<int>(W),
             static_cast<int>(C), alpha, thresh, beta, interval);

@@ -15,8 +15,9 @@
 //
 // Layout: x is [T][B][H][W][C] in memory (a channels-last batch of T*B images), out / g_out are
 // [T][B][H/2][W/2][C]. One thread owns VEC consecutive channels of one pooled position for all T
-// steps; the four window positions are processed one after the other so only one position's T
-// input vectors are live at a time.
+// steps. The loads of all four window positions (4 x T vectors) are issued before any of them is
+// used - processed position by position, each thread went through four dependent rounds of memory
+// latency with only T small loads in flight, and the kernels ran at a quarter of the bandwidth.
 #pragma once
 #include "lif_kernels.cuh"
 
@@ -61,14 +62,22 @@ __global__ void lif_pool_fwd_kernel(const IO* __restrict__ x, IO* __restrict__ o
 #pragma unroll
         for (int v = 0; v < VEC; ++v) acc[t][v] = 0.f;
 
+    Pack<IO, VEC> xin[4][TMAX];
 #pragma unroll
     for (int p = 0; p < 4; ++p) {
         const int h = 2 * ho + (p >> 1), w = 2 * wo + (p & 1);
         const long long off = ((static_cast<long long>(b) * H + h) * W + w) * C + cv * VEC;
-        Pack<IO, VEC> xin[TMAX];
 #pragma unroll
         for (int t = 0; t < TMAX; ++t)
-            if (t < T) xin[t] = ld_stream<IO, VEC>(x + static_cast<long long>(t) * n_full + off);
+            if (t < T) xin[p][t] = ld_stream<IO, VEC>(x + static_cast<long long>(t) * n_full + off);
+    }
+#pragma unroll
+    for (int p = 0; p < 4; ++p)
+#pragma unroll
+        for (int t = 0; t < TMAX; ++t)
+            if (t < T) keep_loaded(xin[p][t]);
+#pragma unroll
+    for (int p = 0; p < 4; ++p) {
         float u[VEC], gate[VEC];
 #pragma unroll
         for (int v = 0; v < VEC; ++v) { u[v] = 0.f; gate[v] = 1.f; }
@@ -78,7 +87,7 @@ __global__ void lif_pool_fwd_kernel(const IO* __restrict__ x, IO* __restrict__ o
 #pragma unroll
                 for (int v = 0; v < VEC; ++v) {
                     const float leak = mul_rn(mul_rn(alpha, u[v]), gate[v]);
-                    u[v] = add_rn(leak, Elem<IO>::load(xin[t].v[v]));
+                    u[v] = add_rn(leak, Elem<IO>::load(xin[p][t].v[v]));
                     const bool s = u[v] > thresh;
                     gate[v] = s ? 0.f : 1.f;
                     acc[t][v] += s ? 0.25f : 0.f;
@@ -121,14 +130,24 @@ __global__ void lif_pool_bwd_kernel(const IO* __restrict__ x, const IO* __restri
             for (int v = 0; v < VEC; ++v) gs[t][v] = mul_rn(Elem<IO>::load(gin.v[v]), 0.25f);
         }
     }
+    Pack<IO, VEC> xin[4][TMAX];
 #pragma unroll
     for (int p = 0; p < 4; ++p) {
         const int h = 2 * ho + (p >> 1), w = 2 * wo + (p & 1);
         const long long off = ((static_cast<long long>(b) * H + h) * W + w) * C + cv * VEC;
-        Pack<IO, VEC> xin[TMAX];
 #pragma unroll
         for (int t = 0; t < TMAX; ++t)
-            if (t < T) xin[t] = ld_stream<IO, VEC>(x + static_cast<long long>(t) * n_full + off);
+            if (t < T) xin[p][t] = ld_stream<IO, VEC>(x + static_cast<long long>(t) * n_full + off);
+    }
+#pragma unroll
+    for (int p = 0; p < 4; ++p)
+#pragma unroll
+        for (int t = 0; t < TMAX; ++t)
+            if (t < T) keep_loaded(xin[p][t]);
+#pragma unroll
+    for (int p = 0; p < 4; ++p) {
+        const int h = 2 * ho + (p >> 1), w = 2 * wo + (p & 1);
+        const long long off = ((static_cast<long long>(b) * H + h) * W + w) * C + cv * VEC;
         float u[TMAX][VEC];
         float uu[VEC], gate[VEC];
 #pragma unroll
@@ -139,7 +158,7 @@ __global__ void lif_pool_bwd_kernel(const IO* __restrict__ x, const IO* __restri
 #pragma unroll
                 for (int v = 0; v < VEC; ++v) {
                     const float leak = mul_rn(mul_rn(alpha, uu[v]), gate[v]);
-                    uu[v] = add_rn(leak, Elem<IO>::load(xin[t].v[v]));
+                    uu[v] = add_rn(leak, Elem<IO>::load(xin[p][t].v[v]));
                     gate[v] = (uu[v] > thresh) ? 0.f : 1.f;
                     u[t][v] = uu[v];
                 }
