@@ -99,13 +99,31 @@ int snn_lif_pool_bwd(const void* x, const void* grad_out, void* grad_x, int64_t 
     if (!x || !grad_out || !grad_x) return SNN_ERR_NULL;
     if (!aligned(x, es) || !aligned(grad_out, es) || !aligned(grad_x, es)) return SNN_ERR_ALIGN;
     int vec = pick_vec(C, es, {x, grad_out, grad_x});
+    // SNN_LIF_POOL_BWD_WINDOW=1: the one-thread-per-window kernel (kept for comparison)
+    static const bool per_window = [] { const char* e = getenv("SNN_LIF_POOL_BWD_WINDOW"); return e && e[0] == '1'; }();
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (!per_window) {
+        // one thread per full-resolution position: 128-thread CTAs, the LIF backward's register budget
+        if (T > 8 && dtype == SNN_F32 && vec > 2) vec = 2;
+        constexpr int kFlatBlock = 128;
+        const long long threads = B * H * W * (C / vec);
+        if ((threads + kFlatBlock - 1) / kFlatBlock > 0x7fffffffLL) return SNN_ERR_SHAPE;
+        const unsigned grid = static_cast<unsigned>((threads + kFlatBlock - 1) / kFlatBlock);
+        dispatch(dtype, vec, static_cast<int>(T), [&](auto io, auto v, auto tm) {
+            using IO = decltype(io);
+            snn::lif_pool_bwd_flat_kernel<IO, decltype(v)::value, decltype(tm)::value><<<grid, kFlatBlock, 0, st>>>(
+                static_cast<const IO*>(x), static_cast<const IO*>(grad_out), static_cast<IO*>(grad_x),
+                static_cast<int>(T), static_cast<int>(B), static_cast<int>(H), static_cast<int>(W),
+                static_cast<int>(C), alpha, thresh, beta, interval);
+        });
+        return launch_status();
+    }
     if (T > 8 && vec > 2) vec = 2;                          // 4 windows x 16 steps of loads + 16 steps of state in registers
     const long long threads = B * (H / 2) * (W / 2) * (C / vec);
     // 128-thread CTAs: at ~160 registers per thread three of them fit an SM, one 256-thread CTA would not
     constexpr int kBwdBlock = 128;
     if ((threads + kBwdBlock - 1) / kBwdBlock > 0x7fffffffLL) return SNN_ERR_SHAPE;
     const unsigned grid = static_cast<unsigned>((threads + kBwdBlock - 1) / kBwdBlock);
-    cudaStream_t st = static_cast<cudaStream_t>(stream);
     dispatch(dtype, vec, static_cast<int>(T), [&](auto io, auto v, auto tm) {
         using IO = decltype(io);
         snn::lif_pool_bwd_kernel<IO, decltype(v)::value, decltype(tm)::value><<<grid, kBwdBlock, 0, st>>>(

@@ -188,4 +188,76 @@ __global__ void lif_pool_bwd_kernel(const IO* __restrict__ x, const IO* __restri
     }
 }
 
+// Backward with one thread per FULL-resolution position (VEC channels, all T steps): the plain LIF
+// reverse pass whose upstream gradient is gathered from the pooled tensor (each pooled vector is read
+// by the four threads of its window; it is a quarter of the bytes and stays in L1 / L2). Four times
+// the threads of the kernel above at ~60 registers each; same arithmetic, same results.
+template <typename IO, int VEC, int TMAX>
+__global__ void lif_pool_bwd_flat_kernel(const IO* __restrict__ x, const IO* __restrict__ g_out,
+                                         IO* __restrict__ gx, int T, int B, int H, int W, int C,
+                                         float alpha, float thresh, float beta, float interval)
+{
+    const int Ho = H / 2, Wo = W / 2, Cv = C / VEC;
+    const long long total = static_cast<long long>(B) * H * W * Cv;
+    const long long id = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (id >= total) return;
+    int cv, w, h, b;
+    decompose(id, total, Cv, W, H, cv, w, h, b);
+    const long long n_full = static_cast<long long>(B) * H * W * C;
+    const long long n_pool = static_cast<long long>(B) * Ho * Wo * C;
+    const long long off = id * VEC;                                    // ((b*H + h)*W + w)*C + cv*VEC
+    const long long o_off = ((static_cast<long long>(b) * Ho + (h >> 1)) * Wo + (w >> 1)) * C + cv * VEC;
+
+    Pack<IO, VEC> xin[TMAX], gin[TMAX];
+#pragma unroll
+    for (int t = 0; t < TMAX; ++t)
+        if (t < T) xin[t] = ld_stream<IO, VEC>(x + static_cast<long long>(t) * n_full + off);
+#pragma unroll
+    for (int t = 0; t < TMAX; ++t)
+        if (t < T) gin[t] = ld_stream<IO, VEC>(g_out + static_cast<long long>(t) * n_pool + o_off);
+#pragma unroll
+    for (int t = 0; t < TMAX; ++t)
+        if (t < T) { keep_loaded(xin[t]); keep_loaded(gin[t]); }
+
+    float u[TMAX][VEC];
+    {
+        float uu[VEC], gate[VEC];
+#pragma unroll
+        for (int v = 0; v < VEC; ++v) { uu[v] = 0.f; gate[v] = 1.f; }
+#pragma unroll
+        for (int t = 0; t < TMAX; ++t) {
+            if (t < T) {
+#pragma unroll
+                for (int v = 0; v < VEC; ++v) {
+                    const float leak = mul_rn(mul_rn(alpha, uu[v]), gate[v]);
+                    uu[v] = add_rn(leak, Elem<IO>::load(xin[t].v[v]));
+                    gate[v] = (uu[v] > thresh) ? 0.f : 1.f;
+                    u[t][v] = uu[v];
+                }
+            }
+        }
+    }
+    float gu[VEC];
+#pragma unroll
+    for (int v = 0; v < VEC; ++v) gu[v] = 0.f;
+#pragma unroll
+    for (int t = TMAX - 1; t >= 0; --t) {
+        if (t < T) {
+            Pack<IO, VEC> o;
+#pragma unroll
+            for (int v = 0; v < VEC; ++v) {
+                const float ut = u[t][v];
+                const float ga = mul_rn(gu[v], alpha);
+                float g1 = 0.f;
+                if (inside_window(ut, thresh, interval))
+                    g1 = sub_rn(mul_rn(Elem<IO>::load(gin[t].v[v]), 0.25f), mul_rn(ga, ut));
+                const float keep = (ut <= thresh) ? 1.f : 0.f;
+                gu[v] = add_rn(mul_rn(g1, beta), mul_rn(ga, keep));
+                o.v[v] = Elem<IO>::store(gu[v]);
+            }
+            st_stream<IO, VEC>(gx + static_cast<long long>(t) * n_full + off, o);
+        }
+    }
+}
+
 }  // namespace snn
