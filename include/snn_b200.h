@@ -197,6 +197,22 @@ int snn_lif_pool_bwd(const void *x, const void *grad_out, void *grad_x, int64_t 
                      float beta, float interval, void *stream);
 
 /* ----------------------------------------------------------------------------------------
+ * LIF of the sum of two currents (residual networks: block output + shortcut, then LIF). No
+ * counterpart in the reference's native table (its residual scripts add with torch and then call
+ * the plain LIF op, snnlib_func.py:22-36). The sum is rounded to the I/O type before it enters
+ * the recurrence, so results equal "a + b in the I/O type, then snn_lif_fwd / snn_lif_bwd" bit for
+ * bit, without the sum ever being written to memory. a, b, spike, grad_spike, grad: [T][N], same
+ * layout; dtype f32 / bf16 / f16.
+ *   forward   spike = LIF(a + b)
+ *   backward  grad  = dL/d(a + b) (= dL/da = dL/db); T <= 16, else SNN_ERR_UNSUPPORTED
+ * -------------------------------------------------------------------------------------- */
+int snn_lif_add_fwd(const void *a, const void *b, void *spike, int64_t T, int64_t N, int dtype,
+                    float alpha, float thresh, void *stream);
+int snn_lif_add_bwd(const void *a, const void *b, const void *grad_spike, void *grad, int64_t T,
+                    int64_t N, int dtype, float alpha, float thresh, float beta, float interval,
+                    void *stream);
+
+/* ----------------------------------------------------------------------------------------
  * Per-channel bias of a synaptic layer. Element (o, c, i) at (o*C + c)*inner + i: inner = 1 for
  * channels-last images and [rows, C] matrices, inner = H*W for contiguous [N, C, H, W].
  *   snn_channel_bias_add   y[o, c, i] += bias[c], in place

@@ -29,6 +29,8 @@ SIGNATURES = {
     "snn_spike_unpack": (_int, [_vp, _vp, _i64, _i64, _int, _vp]),
     "snn_copy_rows_async": (_int, [_vp, _sz, _vp, _sz, _sz, _i64, _int, _vp]),
     "snn_lif_bwd_noalloc": (_int, [_vp, _vp, _vp, _i64, _i64, _int, _f32, _f32, _f32, _f32, _vp]),
+    "snn_lif_add_fwd": (_int, [_vp, _vp, _vp, _i64, _i64, _int, _f32, _f32, _vp]),
+    "snn_lif_add_bwd": (_int, [_vp, _vp, _vp, _vp, _i64, _i64, _int, _f32, _f32, _f32, _f32, _vp]),
     "snn_lif_pool_fwd": (_int, [_vp, _vp, _i64, _i64, _i64, _i64, _i64, _int, _f32, _f32, _vp]),
     "snn_lif_pool_bwd": (_int, [_vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _int, _f32, _f32, _f32, _f32, _vp]),
     "snn_linear_lif_fwd_supported": (_int, [_i64, _i64, _i64, _i64, _int]),
@@ -218,6 +220,54 @@ def lif_bwd(x, grad_spike, alpha, thresh, beta, interval):
         rc = lib().snn_lif_bwd(_ptr(x), _ptr(g), _ptr(gx), T, N, code, float(alpha), float(thresh),
                                float(beta), float(interval), _ptr(ws), need, _stream(x.device))
     check("snn_lif_bwd", rc)
+    return gx
+
+
+LIF_ADD_MAX_T = 16
+
+
+def lif_add_operands(a, b):
+    """(a, b) made time-major dense with IDENTICAL strides (b is copied into a's layout if it
+    differs), after the checks shared by both directions."""
+    _require_cuda(a, "current")
+    _require_cuda(b, "shortcut")
+    if a.shape != b.shape or a.dtype != b.dtype or a.device != b.device:
+        raise ValueError("lif_add: the two currents must agree in shape, dtype and device")
+    a = as_time_major_dense(a)
+    return a, like_layout(b, a)
+
+
+@nvtx_range("snn.lif_add_fwd")
+def lif_add_fwd(a, b, alpha, thresh):
+    """snn_lif_add_fwd: spikes of LIF(a + b) for two [T, ...] tensors already in one layout."""
+    T = a.shape[0]
+    N = a.numel() // T
+    with torch.cuda.device(a.device):
+        spike = torch.empty_like(a)
+        if N == 0:
+            return spike
+        rc = lib().snn_lif_add_fwd(_ptr(a), _ptr(b), _ptr(spike), T, N, DTYPE_CODE[a.dtype], float(alpha),
+                                   float(thresh), _stream(a.device))
+    check("snn_lif_add_fwd", rc)
+    return spike
+
+
+@nvtx_range("snn.lif_add_bwd")
+def lif_add_bwd(a, b, grad_spike, alpha, thresh, beta, interval):
+    """snn_lif_add_bwd: dL/d(a + b), shaped and laid out like a."""
+    _require_cuda(grad_spike, "grad_spike")
+    if grad_spike.shape != a.shape or grad_spike.dtype != a.dtype or grad_spike.device != a.device:
+        raise ValueError("grad_spike must have the currents' shape, dtype and device")
+    g = like_layout(grad_spike, a)
+    T = a.shape[0]
+    N = a.numel() // T
+    with torch.cuda.device(a.device):
+        gx = torch.empty_like(a)
+        if N == 0:
+            return gx
+        rc = lib().snn_lif_add_bwd(_ptr(a), _ptr(b), _ptr(g), _ptr(gx), T, N, DTYPE_CODE[a.dtype], float(alpha),
+                                   float(thresh), float(beta), float(interval), _stream(a.device))
+    check("snn_lif_add_bwd", rc)
     return gx
 
 

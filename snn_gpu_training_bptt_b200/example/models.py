@@ -76,11 +76,12 @@ class SpikingVGG(nn.Module):
 class _ResBlock(nn.Module):
     """conv-LIF-conv, add the shortcut current, LIF (a LIF after every conv and after the add)."""
 
-    def __init__(self, cin, cout, stride):
+    def __init__(self, cin, cout, stride, fused_add=True):
         super().__init__()
+        self.fused_add = fused_add
         self.conv1 = sop.Conv(cin, cout, stride=(stride, stride))
         self.conv2 = sop.FireConv(cout, cout)
-        self.fire = sop.Fire()
+        self.fire = sop.FireAdd() if fused_add else sop.Fire()
         self.short = None
         if stride != 1 or cin != cout:
             self.short = sop.Conv(cin, cout, kernel_size=(1, 1), stride=(stride, stride), padding=(0, 0))
@@ -88,7 +89,7 @@ class _ResBlock(nn.Module):
     def forward(self, spikes):
         cur = self.conv2(self.conv1(spikes))
         skip = spikes if self.short is None else self.short(spikes)
-        return self.fire(cur + skip)
+        return self.fire(cur, skip) if self.fused_add else self.fire(cur + skip)
 
 
 class SpikingResNet19(nn.Module):
@@ -96,7 +97,7 @@ class SpikingResNet19(nn.Module):
     channels (stride 2 between stages), global average pool, fc 512->256 - LIF - fc->classes."""
 
     def __init__(self, time_steps=16, num_classes=10, act_dtype=torch.bfloat16, widths=(128, 256, 512),
-                 blocks=(3, 3, 2), hidden=256, fused_fc=True):
+                 blocks=(3, 3, 2), hidden=256, fused_fc=True, fused_add=True):
         super().__init__()
         self.T, self.act_dtype = time_steps, act_dtype
         self.fused_fc = fused_fc
@@ -105,7 +106,7 @@ class SpikingResNet19(nn.Module):
         layers, cin = [], widths[0]
         for stage, (w, n) in enumerate(zip(widths, blocks)):
             for b in range(n):
-                layers.append(_ResBlock(cin, w, 2 if (b == 0 and stage > 0) else 1))
+                layers.append(_ResBlock(cin, w, 2 if (b == 0 and stage > 0) else 1, fused_add))
                 cin = w
         self.blocks = nn.ModuleList(layers)
         self.fc1 = sop.FcFire(cin, hidden) if fused_fc else sop.Fc(cin, hidden)

@@ -51,6 +51,31 @@ class FireFunc(torch.autograd.Function):
 fire_func = FireFunc.apply
 
 
+class FireAddFunc(torch.autograd.Function):
+    """spike = LIF(current + shortcut) without the sum in memory (an addition to the reference's set
+    of Functions; equals ``fire_func(current + shortcut)`` bit for bit, spikes and gradients)."""
+
+    @staticmethod
+    def forward(ctx, current, shortcut):
+        current, shortcut = _capi.lif_add_operands(current, shortcut)
+        ctx.save_for_backward(current, shortcut)
+        return _capi.lif_add_fwd(current, shortcut, alpha, thresh)
+
+    @staticmethod
+    def backward(ctx, grad_spike):
+        current, shortcut = ctx.saved_tensors
+        grad = _capi.lif_add_bwd(current, shortcut, grad_spike, alpha, thresh, beta, interval)
+        return (grad if ctx.needs_input_grad[0] else None, grad if ctx.needs_input_grad[1] else None)
+
+
+def fire_add_func(current, shortcut):
+    """LIF of the sum of two currents; falls back to add -> ``fire_func`` where the fused backward
+    does not apply (more than 16 time steps, float64)."""
+    if current.shape[0] > _capi.LIF_ADD_MAX_T or current.dtype == torch.float64:
+        return fire_func(current + shortcut)
+    return FireAddFunc.apply(current, shortcut)
+
+
 class FirePoolFunc(torch.autograd.Function):
     """LIF followed by AvgPool2d(2) on every time step, as one kernel each way (an addition to the
     reference's set of Functions; equals ``avg_pool2d(fire_func(x))`` applied per time step)."""

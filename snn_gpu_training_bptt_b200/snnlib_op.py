@@ -27,6 +27,14 @@ class Fire(nn.Module):
         return sf.fire_func(x)
 
 
+class FireAdd(nn.Module):
+    """LIF layer on the sum of two currents, fused (not in the reference's layer set; identical to
+    ``Fire()(current + shortcut)``)."""
+
+    def forward(self, current, shortcut):
+        return sf.fire_add_func(current, shortcut)
+
+
 class FirePool(nn.Module):
     """LIF layer followed by AvgPool2d(2) per time step, fused (not in the reference's layer set;
     numerically identical to ``Fire`` then pooling each x[t])."""

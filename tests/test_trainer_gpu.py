@@ -208,6 +208,49 @@ def test_fused_lif_pool_equals_lif_then_pool(dtype, shape):
         assert np.array_equal(b.grad.cpu().numpy(), orc.c_lif_bwd(x.numpy(), np.ascontiguousarray(g_full)))
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("shape", [(8, 2, 16, 8, 8), (6, 3, 5, 3, 7), (16, 1, 8, 4, 4), (4, 2, 131), (1, 1, 3), (11, 4, 64, 2, 2)])
+def test_fused_lif_of_a_sum_equals_add_then_lif(dtype, shape):
+    """FireAdd(a, b) == Fire(a + b) bit for bit, spikes and both input gradients (odd sizes take the
+    narrow-vector kernels, T not in {4, 8, 16} the guarded ones); in fp32 also equal to the CPU
+    oracle applied to the rounded sum. One addend may arrive channels-last, the other contiguous."""
+    from snn_gpu_training_bptt_b200 import snnlib_func as sf
+    gen = torch.Generator().manual_seed(sum(shape) + 1)
+    x = (0.3 + torch.randn(shape, generator=gen)).to(dtype)
+    y = (0.2 + 0.7 * torch.randn(shape, generator=gen)).to(dtype)
+    g = torch.randn(shape, generator=gen).to(dtype)
+    a1, b1 = x.cuda().requires_grad_(True), y.cuda().requires_grad_(True)
+    a2, b2 = x.cuda().requires_grad_(True), y.cuda().requires_grad_(True)
+    b2_in = b2
+    if len(shape) == 5:                       # same values, channels-last strides
+        b2_in = b2.view(-1, *shape[2:]).contiguous(memory_format=torch.channels_last).view(shape)
+    want = sf.fire_func(a1 + b1)
+    got = sf.fire_add_func(a2, b2_in)
+    assert torch.equal(want, got)
+    want.backward(g.cuda())
+    got.backward(g.cuda())
+    assert torch.equal(a1.grad, a2.grad) and torch.equal(b1.grad, b2.grad)
+    assert torch.equal(a2.grad, b2.grad)
+    if dtype == torch.float32:
+        total = (x + y).numpy()
+        assert np.array_equal(got.detach().cpu().numpy(), orc.c_lif_fwd(total)[0])
+        assert np.array_equal(a2.grad.cpu().numpy(), orc.c_lif_bwd(total, g.numpy()))
+
+
+def test_lif_of_a_sum_fallback_and_errors():
+    from snn_gpu_training_bptt_b200 import _capi, snnlib_func as sf
+    x = torch.randn(20, 2, 33, device="cuda")            # 20 steps: add -> LIF composition
+    y = torch.randn(20, 2, 33, device="cuda")
+    assert torch.equal(sf.fire_add_func(x, y), sf.fire_func(x + y))
+    with pytest.raises(ValueError):
+        sf.fire_add_func(x[:4], y[:5])
+    with pytest.raises(_capi.SnnError):
+        _capi.lif_add_bwd(x, y, x, 0.3, 0.5, 1.0, 0.5)    # the native backward itself refuses T > 16
+    only_a = x[:8].clone().requires_grad_(True)
+    sf.fire_add_func(only_a, y[:8]).sum().backward()     # shortcut without gradient
+    assert only_a.grad is not None
+
+
 def test_fused_and_unfused_pool_networks_agree():
     from snn_gpu_training_bptt_b200.example import models
     images = torch.rand(2, 3, 16, 16, device="cuda")
