@@ -773,6 +773,47 @@ def run_bn_lif(args):
         del x, g, out, gx
 
 
+def run_lif_add(args):
+    """LIF of a sum of two currents (residual blocks), fused kernels against add -> LIF, one line per
+    (dtype, T); N = 2^(log2n - 2) neurons so that every tensor is larger than L2."""
+    import torch
+    from snn_gpu_training_bptt_b200 import _capi
+    peak, peak_src = measured_peak()
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    N = 1 << (args.log2n - 2)
+    reps = args.steps if args.steps < 50 else 20
+    for dtype, name in ((torch.bfloat16, "bf16"), (torch.float32, "f32")):
+        for T in (8, 16):
+            gen = torch.Generator(device=dev).manual_seed(1234)
+            a = (torch.randn((T, N), device=dev, generator=gen) * 0.7 + 0.3).to(dtype)
+            b = (torch.randn((T, N), device=dev, generator=gen) * 0.7 + 0.2).to(dtype)
+            g = torch.randn((T, N), device=dev, generator=gen).to(dtype)
+            total = a + b
+            spike = _capi.lif_add_fwd(a, b, ALPHA, THRESH)
+            grad = _capi.lif_add_bwd(a, b, g, ALPHA, THRESH, BETA, INTERVAL)
+            same = bool(torch.equal(spike, _capi.lif_fwd(total, ALPHA, THRESH)[0])
+                        and torch.equal(grad, _capi.lif_bwd(total, g, ALPHA, THRESH, BETA, INTERVAL)))
+            del spike, grad
+            t_ff = _time_kernel(lambda: _capi.lif_add_fwd(a, b, ALPHA, THRESH), reps)
+            t_fb = _time_kernel(lambda: _capi.lif_add_bwd(a, b, g, ALPHA, THRESH, BETA, INTERVAL), reps)
+            t_uf = _time_kernel(lambda: _capi.lif_fwd(torch.add(a, b, out=total), ALPHA, THRESH), reps)
+            t_ub = _time_kernel(lambda: _capi.lif_bwd(total, g, ALPHA, THRESH, BETA, INTERVAL), reps)
+            es = a.element_size()
+            gb = lambda elems, ms: elems * es * T * N / ms / 1e6
+            print(json.dumps({
+                "metric": "lif_add_fwd_bwd_hbm_gbps", "value": round(gb(7, t_ff + t_fb), 1), "unit": "GB/s", "dtype": name,
+                "config": {"workload": f"LIF(a + b) fused fwd + bwd, {name}, T={T}, N=2^{args.log2n - 2}",
+                           "elements_per_neuron_step": "fused fwd 3, bwd 4; unfused add 3 + fwd 2, bwd 3",
+                           "l2": "every tensor larger than L2"},
+                "equals_add_then_lif": same,
+                "fwd_ms": round(t_ff, 4), "fwd_gbs": round(gb(3, t_ff), 1), "bwd_ms": round(t_fb, 4),
+                "bwd_gbs": round(gb(4, t_fb), 1), "unfused_add_fwd_ms": round(t_uf, 4), "unfused_bwd_ms": round(t_ub, 4),
+                "fused_over_unfused_time": round((t_ff + t_fb) / (t_uf + t_ub), 4),
+                "frac_of_peak": round(gb(7, t_ff + t_fb) / peak, 4), "peak": peak, "peak_source": peak_src}))
+            del a, b, g, total
+
+
 def bf16_peak_tflops():
     try:
         with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
@@ -906,7 +947,7 @@ def main():
     ap.add_argument("--trainer-steps", type=int, default=30)
     ap.add_argument("--log2n", type=int, default=26,
                     help="log2 of neurons per GPU (26 = the benchmark size; smaller only for profiler captures)")
-    ap.add_argument("--workload", default="lif", choices=["lif", "sweep", "bn_lif", "linear_lif", "host_link"],
+    ap.add_argument("--workload", default="lif", choices=["lif", "sweep", "bn_lif", "linear_lif", "host_link", "lif_add"],
                     help="lif = the benchmark line; the others are secondary single-GPU measurements")
     args = ap.parse_args()
     if args.impl == "reference":
@@ -919,6 +960,8 @@ def main():
         run_linear_lif(args)
     elif args.workload == "host_link":
         run_host_link(args)
+    elif args.workload == "lif_add":
+        run_lif_add(args)
     else:
         run_ours(args)
 
