@@ -60,6 +60,15 @@ def test_argument_validation_needs_no_gpu(built_lib):
     assert L.snn_lif_bwd_workspace_bytes(33, 1000, 1) == 33 * 1000 * 4
     assert L.snn_lif_bwd_workspace_bytes(64, 10, 3) == 64 * 10 * 8
     assert L.snn_lif_bwd_workspace_bytes(0, 10, 0) == -2
+    # LIF of a sum
+    assert L.snn_lif_add_fwd(fake, None, fake, 8, 16, 0, 0.25, 0.25, None) == 1                  # NULL shortcut
+    assert L.snn_lif_add_fwd(fake, fake, fake, 0, 16, 0, 0.25, 0.25, None) == 2
+    assert L.snn_lif_add_fwd(fake, fake, fake, 8, 16, 3, 0.25, 0.25, None) == 5                  # no float64 form
+    assert L.snn_lif_add_fwd(fake, odd, fake, 8, 16, 0, 0.25, 0.25, None) == 4
+    assert L.snn_lif_add_fwd(fake, fake, fake, 8, 0, 0, 0.25, 0.25, None) == 0
+    assert L.snn_lif_add_bwd(fake, fake, None, fake, 8, 16, 1, 0.25, 0.25, 1.0, 0.5, None) == 1
+    assert L.snn_lif_add_bwd(fake, fake, fake, fake, 17, 16, 1, 0.25, 0.25, 1.0, 0.5, None) == 5  # T beyond the register form
+    assert L.snn_lif_add_bwd(fake, fake, fake, fake, 8, 16, 9, 0.25, 0.25, 1.0, 0.5, None) == 3
     # unpack
     assert L.snn_spike_unpack(None, fake, 8, 16, 0, None) == 1
     assert L.snn_spike_unpack(fake, fake, 40, 16, 0, None) == 5
@@ -111,6 +120,9 @@ def test_cpu_tensors_are_rejected(built_lib):
         snnlib.fire_s_fp(x, 0.25, 0.25)
     with pytest.raises(ValueError, match="CUDA"):
         snnlib.fire_bp(x, x, 0.25, 0.25, 1.0, 0.5)
+    from snn_gpu_training_bptt_b200 import snnlib_func as sf
+    with pytest.raises(ValueError, match="CUDA"):
+        sf.fire_add_func(x, x)
 
 
 def test_linear_lif_backward_host_logic(built_lib):
