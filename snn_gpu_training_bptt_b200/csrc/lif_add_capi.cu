@@ -2,6 +2,8 @@
 #include "../../include/snn_b200.h"
 #include "lif_add_kernels.cuh"
 
+#include <cstdint>
+#include <initializer_list>
 #include <type_traits>
 
 namespace snn_internal {
